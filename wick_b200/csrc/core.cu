@@ -1,0 +1,265 @@
+// Row-wise kernels of the decoder: embedding gather, RMSNorm (optionally fused
+// with the residual addition and with a row gather), rotary tables, the fused
+// per-head norm + rotation + cache append, and SwiGLU on separate arrays.
+//
+// All arithmetic is float32; T is the storage type of activations (bfloat16 or
+// float).  Formulas: wick src/kernels.rs:343-357 (rms norm: sum of squares over
+// the row, divided by its length, scale = 1/sqrt(ss+eps), (x*scale)*w),
+// src/model.rs:404-414 (half-split rotation by pos*inv_freq[i]),
+// src/model.rs:475-483 (norm, then rotation, then the cache write),
+// src/kernels.rs:374-378 (g/(1+exp(-g))*u).
+#include "common.cuh"
+
+namespace wick {
+
+constexpr int kPage = 64;
+
+// ---- embedding -------------------------------------------------------------
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
+                             float* __restrict__ out, int width) {
+    const int64_t row = blockIdx.x;
+    const T* src = table + (int64_t)tokens[row] * width;
+    float* dst = out + row * width;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) dst[j] = ld(src + j);
+}
+
+// ---- RMSNorm ---------------------------------------------------------------
+// One block per output row i.  Source row r = rows ? rows[i] : i.  If delta is
+// given, x[r] += delta[0][r] + delta[1][r] + ... (index order) and is written
+// back before it is normalised.
+template <typename TOut>
+__global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int splits,
+                               int64_t split_stride, const float* __restrict__ w, float eps,
+                               const int* __restrict__ rows, TOut* __restrict__ out, int width) {
+    extern __shared__ float smem[];
+    float* row = smem;
+    float* red = smem + width;
+    const int i = blockIdx.x;
+    const int64_t r = rows ? rows[i] : i;
+    float* xr = x + r * width;
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+        float v = xr[j];
+        if (delta) {
+            for (int s = 0; s < splits; ++s) v += delta[s * split_stride + r * width + j];
+            xr[j] = v;
+        }
+        row[j] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+    TOut* o = out + (int64_t)i * width;
+    for (int j = threadIdx.x; j < width; j += blockDim.x) st(o + j, (row[j] * scale) * w[j]);
+}
+
+// x[r] += sum of delta for every row (no norm): resolves a pending residual.
+__global__ void add_delta_kernel(float* __restrict__ x, const float* __restrict__ delta, int splits,
+                                 int64_t split_stride, int64_t n) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float v = x[i];
+    for (int s = 0; s < splits; ++s) v += delta[s * split_stride + i];
+    x[i] = v;
+}
+
+// ---- rotary tables ---------------------------------------------------------
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                  float* __restrict__ cos_t, float* __restrict__ sin_t, int n, int half) {
+    int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (int64_t)n * half) return;
+    const int t = idx / half, i = idx % half;
+    const float angle = (float)positions[t] * inv_freq[i];
+    float s, c;
+    sincosf(angle, &s, &c);
+    cos_t[idx] = c;
+    sin_t[idx] = s;
+}
+
+// ---- per-head norm + rotation + cache append --------------------------------
+// One warp per (token, head) vector of the fused projection output
+// qkv[token] = [q heads | k heads | v heads].  q goes to q_out, k and v go to the
+// token's place in its sequence's cache page.
+template <typename T>
+__global__ void qk_norm_rope_append_kernel(
+    const T* __restrict__ qkv, int n_tokens, int n_heads, int n_kv, int hd,
+    const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+    const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+    T* __restrict__ q_out, T* __restrict__ kv, const int* __restrict__ page_table, int table_width,
+    const int* __restrict__ seq_of_token, const int* __restrict__ positions, int write_kv) {
+    const int lane = threadIdx.x & 31;
+    const int heads_total = n_heads + (write_kv ? 2 * n_kv : 0);
+    const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= (int64_t)n_tokens * heads_total) return;
+    const int t = item / heads_total, h = item % heads_total;
+    const int half = hd >> 1;
+    const int row_width = (n_heads + 2 * n_kv) * hd;
+    const T* src = qkv + (int64_t)t * row_width + (int64_t)h * hd;
+
+    T* dst;
+    const float* w = nullptr;
+    bool rotate = true;
+    if (h < n_heads) {
+        dst = q_out + ((int64_t)t * n_heads + h) * hd;
+        w = q_w;
+    } else {
+        const int is_v = h >= n_heads + n_kv;
+        const int kh = h - n_heads - (is_v ? n_kv : 0);
+        const int pos = positions[t];
+        const int page = page_table[(int64_t)seq_of_token[t] * table_width + pos / kPage];
+        dst = kv + ((((int64_t)page * 2 + is_v) * n_kv + kh) * kPage + (pos % kPage)) * hd;
+        w = is_v ? nullptr : k_w;
+        rotate = !is_v;
+        if (is_v) {
+            for (int i = lane; i < hd; i += 32) dst[i] = src[i];
+            return;
+        }
+    }
+    float ss = 0.f;
+    for (int i = lane; i < hd; i += 32) {
+        const float v = ld(src + i);
+        ss += v * v;
+    }
+    float scale = 1.f;
+    if (w) {
+        ss = warp_sum(ss);
+        scale = 1.0f / sqrtf(ss / (float)hd + eps);
+    }
+    for (int i = lane; i < half; i += 32) {
+        float a = ld(src + i), b = ld(src + i + half);
+        if (w) {
+            a = (a * scale) * w[i];
+            b = (b * scale) * w[i + half];
+        }
+        if (rotate && cos_t) {
+            const float c = cos_t[(int64_t)t * half + i], s = sin_t[(int64_t)t * half + i];
+            const float ra = a * c - b * s, rb = b * c + a * s;
+            a = ra;
+            b = rb;
+        }
+        st(dst + i, a);
+        st(dst + i + half, b);
+    }
+}
+
+// ---- SwiGLU on separate arrays ----------------------------------------------
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gate, const T* __restrict__ up, T* __restrict__ out,
+                                int64_t n) {
+    int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float g = ld(gate + i), u = ld(up + i);
+    st(out + i, g / (1.0f + expf(-g)) * u);
+}
+
+template <typename T>
+int embed(const void* table, const int* tokens, float* out, int n, int width, int64_t vocab, cudaStream_t s) {
+    WICK_REQUIRE(n >= 0 && width > 0 && vocab > 0, "embed: bad sizes n=%d width=%d", n, width);
+    if (n == 0) return 0;
+    embed_kernel<T><<<n, 256, 0, s>>>((const T*)table, tokens, out, width);
+    return check_launch("embed");
+}
+
+template <typename TOut>
+int rmsnorm(float* x, const float* delta, int splits, int64_t n_rows_x, const float* w, float eps,
+            const int* rows, void* out, int n_out, int width, cudaStream_t s) {
+    WICK_REQUIRE(width > 0 && n_out >= 0, "rmsnorm: bad sizes");
+    if (n_out == 0) return 0;
+    const size_t smem = ((size_t)width + 40) * sizeof(float);
+    WICK_REQUIRE(smem <= 200 * 1024, "rmsnorm: width %d is beyond the %d that one block's shared memory holds",
+                 width, 200 * 1024 / 4 - 40);
+    static bool raised = false;
+    if (smem > 48 * 1024 && !raised) {
+        WICK_CUDA(cudaFuncSetAttribute(rmsnorm_kernel<TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        raised = true;
+    }
+    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    rmsnorm_kernel<TOut><<<n_out, threads, smem, s>>>(x, delta, splits, n_rows_x * width, w, eps, rows,
+                                                      (TOut*)out, width);
+    return check_launch("rmsnorm");
+}
+
+}  // namespace wick
+
+using namespace wick;
+typedef __nv_bfloat16 bf16;
+
+WICK_API const char* wick_last_error() { return error_buffer(); }
+
+WICK_API int wick_embed_bf16(const void* table, const int* tokens, float* out, int n, int width, int64_t vocab, void* s) {
+    return embed<bf16>(table, tokens, out, n, width, vocab, (cudaStream_t)s);
+}
+WICK_API int wick_embed_f32(const void* table, const int* tokens, float* out, int n, int width, int64_t vocab, void* s) {
+    return embed<float>(table, tokens, out, n, width, vocab, (cudaStream_t)s);
+}
+
+// x: float32 [n_rows_x, width] (updated in place when delta is given);
+// delta: float32 [splits, n_rows_x, width] or null; rows: int32 [n_out] or null
+// (then n_out == n_rows_x); out: [n_out, width].
+WICK_API int wick_rmsnorm_bf16(float* x, const float* delta, int splits, int64_t n_rows_x, const float* w, float eps,
+                               const int* rows, void* out, int n_out, int width, void* s) {
+    return rmsnorm<bf16>(x, delta, splits, n_rows_x, w, eps, rows, out, n_out, width, (cudaStream_t)s);
+}
+WICK_API int wick_rmsnorm_f32(float* x, const float* delta, int splits, int64_t n_rows_x, const float* w, float eps,
+                              const int* rows, void* out, int n_out, int width, void* s) {
+    return rmsnorm<float>(x, delta, splits, n_rows_x, w, eps, rows, out, n_out, width, (cudaStream_t)s);
+}
+
+WICK_API int wick_add_delta(float* x, const float* delta, int splits, int64_t n, void* s) {
+    if (n == 0) return 0;
+    add_delta_kernel<<<ceil_div(n, 256), 256, 0, (cudaStream_t)s>>>(x, delta, splits, n, n);
+    return check_launch("add_delta");
+}
+
+WICK_API int wick_rope_table(const int* positions, const float* inv_freq, float* cos_t, float* sin_t, int n,
+                             int half, void* s) {
+    if (n == 0 || half == 0) return 0;
+    rope_table_kernel<<<ceil_div((int64_t)n * half, 256), 256, 0, (cudaStream_t)s>>>(positions, inv_freq, cos_t,
+                                                                                     sin_t, n, half);
+    return check_launch("rope_table");
+}
+
+template <typename T>
+static int qk_norm_rope_append(const void* qkv, int n_tokens, int n_heads, int n_kv, int hd, const float* q_w,
+                               const float* k_w, float eps, const float* cos_t, const float* sin_t, void* q_out,
+                               void* kv, const int* page_table, int table_width, const int* seq_of_token,
+                               const int* positions, int write_kv, cudaStream_t s) {
+    WICK_REQUIRE(hd > 0 && hd % 2 == 0, "qk_norm_rope_append: head_dim %d must be even", hd);
+    WICK_REQUIRE(n_heads > 0 && n_kv > 0, "qk_norm_rope_append: bad head counts");
+    if (n_tokens == 0) return 0;
+    const int heads_total = n_heads + (write_kv ? 2 * n_kv : 0);
+    const int warps = 4;
+    qk_norm_rope_append_kernel<T><<<ceil_div((int64_t)n_tokens * heads_total, warps), warps * 32, 0, s>>>(
+        (const T*)qkv, n_tokens, n_heads, n_kv, hd, q_w, k_w, eps, cos_t, sin_t, (T*)q_out, (T*)kv, page_table,
+        table_width, seq_of_token, positions, write_kv);
+    return check_launch("qk_norm_rope_append");
+}
+
+WICK_API int wick_qk_norm_rope_append_bf16(const void* qkv, int n_tokens, int n_heads, int n_kv, int hd,
+                                           const float* q_w, const float* k_w, float eps, const float* cos_t,
+                                           const float* sin_t, void* q_out, void* kv, const int* page_table,
+                                           int table_width, const int* seq_of_token, const int* positions,
+                                           int write_kv, void* s) {
+    return qk_norm_rope_append<bf16>(qkv, n_tokens, n_heads, n_kv, hd, q_w, k_w, eps, cos_t, sin_t, q_out, kv,
+                                     page_table, table_width, seq_of_token, positions, write_kv, (cudaStream_t)s);
+}
+WICK_API int wick_qk_norm_rope_append_f32(const void* qkv, int n_tokens, int n_heads, int n_kv, int hd,
+                                          const float* q_w, const float* k_w, float eps, const float* cos_t,
+                                          const float* sin_t, void* q_out, void* kv, const int* page_table,
+                                          int table_width, const int* seq_of_token, const int* positions,
+                                          int write_kv, void* s) {
+    return qk_norm_rope_append<float>(qkv, n_tokens, n_heads, n_kv, hd, q_w, k_w, eps, cos_t, sin_t, q_out, kv,
+                                      page_table, table_width, seq_of_token, positions, write_kv, (cudaStream_t)s);
+}
+
+WICK_API int wick_silu_mul_bf16(const void* g, const void* u, void* out, int64_t n, void* s) {
+    if (n == 0) return 0;
+    silu_mul_kernel<bf16><<<ceil_div(n, 256), 256, 0, (cudaStream_t)s>>>((const bf16*)g, (const bf16*)u, (bf16*)out, n);
+    return check_launch("silu_mul");
+}
+WICK_API int wick_silu_mul_f32(const void* g, const void* u, void* out, int64_t n, void* s) {
+    if (n == 0) return 0;
+    silu_mul_kernel<float><<<ceil_div(n, 256), 256, 0, (cudaStream_t)s>>>((const float*)g, (const float*)u, (float*)out, n);
+    return check_launch("silu_mul");
+}

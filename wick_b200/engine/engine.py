@@ -1,0 +1,277 @@
+"""The engine: a model, its cache, and ONE step function.
+
+``Engine.step(slots, tokens, want)`` runs a batch of sequences that start
+together: in their first step each brings its whole prompt (unequal lengths, all
+tokens flat in one batch), afterwards one token each.  Only the tokens given are
+run; everything earlier comes from the cache.  The logits of the wanted places
+come back as one float32 tensor.  A step of one token per sequence is replayed
+from a captured CUDA graph (one graph per padded batch size); padded entries
+read and write the reserved page 0 and change no real sequence's result.
+
+Reference: wick ``src/model.rs:420-516`` (``Model::forward``: tokens at positions
+``cache.len..``, cache append before attention, length advanced once after all
+layers, logits of the last or of all tokens) generalised from one sequence to a
+batch.
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..cache import PAGE, Cache
+from ..config.base import ModelConfig, get_architecture, load_config
+from ..models.model import Model
+from ..weights.loader import load_weights
+from ..weights.random_init import random_fetch
+from .batch import BatchLayout, StepBatch, fill_host, n_q_tiles
+
+_DTYPES = {"bf16": torch.bfloat16, "bfloat16": torch.bfloat16, "f32": torch.float32, "float32": torch.float32,
+           torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+def parse_dtype(d) -> torch.dtype:
+    try:
+        return _DTYPES[d]
+    except KeyError:
+        raise ValueError(f"unknown dtype {d} (bfloat16 or float32)") from None
+
+
+class Workspace:
+    """Named scratch buffers that grow on demand and are reused across steps."""
+
+    def __init__(self, device):
+        self.device = device
+        self.buffers: Dict[str, torch.Tensor] = {}
+        self.frozen = False
+
+    def get(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        b = self.buffers.get(name)
+        if b is None or b.numel() < numel or b.dtype != dtype:
+            if self.frozen:
+                raise RuntimeError(f"scratch buffer {name} would have to grow to {numel} elements while a CUDA "
+                                   f"graph is being captured")
+            b = self.buffers[name] = torch.empty(max(numel, 1), dtype=dtype, device=self.device)
+        return b
+
+
+class _Staging:
+    """Pinned host buffers for the packed batch description, used in turn."""
+
+    def __init__(self, n: int = 4):
+        self.bufs: List[Optional[torch.Tensor]] = [None] * n
+        self.events: List[Optional[torch.cuda.Event]] = [None] * n
+        self.i = 0
+
+    def take(self, size: int) -> Tuple[torch.Tensor, int]:
+        i = self.i
+        self.i = (i + 1) % len(self.bufs)
+        if self.events[i] is not None:
+            self.events[i].synchronize()
+        b = self.bufs[i]
+        if b is None or b.numel() < size:
+            b = self.bufs[i] = torch.empty(max(size, 1024), dtype=torch.int32, pin_memory=True)
+        return b, i
+
+    def mark(self, i: int) -> None:
+        ev = self.events[i] or torch.cuda.Event()
+        ev.record()
+        self.events[i] = ev
+
+
+class _DecodeGraph:
+    def __init__(self, n_pad: int, table_width: int):
+        self.n_pad, self.table_width = n_pad, table_width
+        self.layout = BatchLayout(n_pad, n_pad, table_width, n_pad, n_pad)
+        self.buffer: Optional[torch.Tensor] = None
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+
+
+class Engine:
+    def __init__(self, model: Model, *, max_tokens: int, max_seqs: Optional[int] = None,
+                 use_graphs: Optional[bool] = None):
+        if model.ctx.device.type != "cuda":
+            raise RuntimeError("the engine runs on a CUDA device only (there is no CPU path)")
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device is available")
+        self.model = model
+        self.spec = model.spec
+        self.device = model.ctx.device
+        self.dtype = model.ctx.dtype
+        self.cache = Cache(model.cache_needs(), max_tokens=max_tokens, dtype=self.dtype, device=self.device,
+                           max_seqs=max_seqs, max_position=self.spec.max_position)
+        self.workspace = Workspace(self.device)
+        self._staging = _Staging()
+        if use_graphs is None:
+            use_graphs = os.environ.get("WICK_B200_NO_GRAPHS", "") == ""
+        self.use_graphs = use_graphs
+        self._graphs: Dict[Tuple[int, int], _DecodeGraph] = {}
+        self.kernel_launches = 0
+
+    # ---- construction ----------------------------------------------------
+    @classmethod
+    def from_dir(cls, model_dir: str, *, dtype="bfloat16", max_tokens: int = 4096, device="cuda:0", **kw) -> "Engine":
+        cfg = load_config(model_dir)
+        arch = get_architecture(cfg.architecture)
+        model = Model(arch.build_spec(cfg), parse_dtype(dtype), device)
+        load_weights(model, model_dir)
+        eng = cls(model, max_tokens=max_tokens, **kw)
+        eng.config = cfg
+        return eng
+
+    @classmethod
+    def from_config(cls, cfg: ModelConfig, seed: int, *, dtype="bfloat16", max_tokens: int = 4096, device="cuda:0",
+                    **kw) -> "Engine":
+        """Random weights drawn on the device (no files)."""
+        arch = get_architecture(cfg.architecture)
+        model = Model(arch.build_spec(cfg), parse_dtype(dtype), device)
+        model.load(random_fetch(model, seed))
+        eng = cls(model, max_tokens=max_tokens, **kw)
+        eng.config = cfg
+        return eng
+
+    # ---- sequences ---------------------------------------------------------
+    def open_seq(self) -> int:
+        return self.cache.open_seq()
+
+    def close_seq(self, slot: int) -> None:
+        self.cache.close_seq(slot)
+
+    def seq_len(self, slot: int) -> int:
+        return self.cache.length(slot)
+
+    # ---- the step ------------------------------------------------------------
+    def _check(self, slots, tokens, want) -> None:
+        if not (len(slots) == len(tokens) == len(want)):
+            raise ValueError("slots, tokens and want must have one entry per sequence")
+        if len(set(slots)) != len(slots):
+            raise ValueError("a slot appears twice in one step")
+        vocab = self.spec.vocab
+        for b, (s, t, w) in enumerate(zip(slots, tokens, want)):
+            if len(t) == 0:
+                raise ValueError(f"sequence {b} (slot {s}) brings no token")
+            lo, hi = min(t), max(t)
+            if lo < 0 or hi >= vocab:
+                raise ValueError(f"token id {lo if lo < 0 else hi} of sequence {b} is outside the vocabulary "
+                                 f"of {vocab}")
+            for i in w:
+                if not 0 <= i < len(t):
+                    raise ValueError(f"wanted place {i} of sequence {b} is outside its {len(t)} tokens")
+
+    def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]],
+             want: Optional[Sequence[Sequence[int]]] = None) -> torch.Tensor:
+        """Run ``tokens[b]`` after what slot ``slots[b]`` already holds.
+
+        want[b]: indices into tokens[b] whose logits are returned (default: the
+        last one).  Returns float32 [sum(len(want[b])), vocab], rows in the order
+        of the sequences and of ``want``."""
+        if want is None:
+            want = [[len(t) - 1] for t in tokens]
+        self._check(slots, tokens, want)
+        cache = self.cache
+        starts = [cache.length(s) for s in slots]
+        for s, st, t in zip(slots, starts, tokens):
+            cache.reserve(s, st + len(t))
+        q_lens = [len(t) for t in tokens]
+        decode = all(q == 1 for q in q_lens)
+        if decode and self.use_graphs:
+            logits = self._step_graph(slots, tokens, want, starts)
+        else:
+            logits = self._step_eager(slots, tokens, want, starts, q_lens)
+        for s, q in zip(slots, q_lens):
+            cache.advance(s, q)
+        return logits
+
+    def _upload(self, layout: BatchLayout, dev: Optional[torch.Tensor], **fields) -> Tuple[torch.Tensor, np.ndarray]:
+        host, idx = self._staging.take(layout.size)
+        arr = host.numpy()[:layout.size]
+        fill_host(layout, arr, **fields)
+        if dev is None:
+            dev = torch.empty(layout.size, dtype=torch.int32, device=self.device)
+        dev.copy_(host[:layout.size], non_blocking=True)
+        self._staging.mark(idx)
+        return dev, arr
+
+    def _step_eager(self, slots, tokens, want, starts, q_lens) -> torch.Tensor:
+        cache = self.cache
+        B = len(slots)
+        kv_lens = [s + q for s, q in zip(starts, q_lens)]
+        width = max(1, max((k + PAGE - 1) // PAGE for k in kv_lens))
+        layout = BatchLayout(B, sum(q_lens), width, sum(len(w) for w in want), n_q_tiles(q_lens))
+        pages = [cache.pages_of(s)[:(k + PAGE - 1) // PAGE] for s, k in zip(slots, kv_lens)]
+        dev, _ = self._upload(layout, None, tokens=tokens, starts=starts, slots=slots, pages=pages, want=want)
+        batch = StepBatch(layout, dev, q_lens=q_lens, starts=starts)
+        batch.workspace = self.workspace
+        batch.kv_bound = batch.max_kv_len
+        return self.model.forward(batch, cache)
+
+    # ---- captured decode -------------------------------------------------------
+    @staticmethod
+    def _bucket(n: int) -> int:
+        b = 1
+        while b < n:
+            b *= 2
+        return b
+
+    def _step_graph(self, slots, tokens, want, starts) -> torch.Tensor:
+        cache = self.cache
+        B = len(slots)
+        n_pad = self._bucket(B)
+        max_pages = max((s + 1 + PAGE - 1) // PAGE for s in starts)
+        width = 8
+        while width < max_pages:
+            width *= 2
+        key = (n_pad, width)
+        g = self._graphs.get(key)
+        if g is None:
+            g = self._graphs[key] = _DecodeGraph(n_pad, width)
+            g.buffer = torch.zeros(g.layout.size, dtype=torch.int32, device=self.device)
+        pad = n_pad - B
+        # Padded entries: one token (id 0) at position 0 of the reserved page 0 / slot 0.
+        f_tokens = [list(t) for t in tokens] + [[0]] * pad
+        f_starts = list(starts) + [0] * pad
+        f_slots = list(slots) + [0] * pad
+        f_pages = [cache.pages_of(s)[:(st + 1 + PAGE - 1) // PAGE] for s, st in zip(slots, starts)] + [[0]] * pad
+        f_want = [[0]] * n_pad            # the graph always computes every row's logits
+        self._upload(g.layout, g.buffer, tokens=f_tokens, starts=f_starts, slots=f_slots, pages=f_pages, want=f_want)
+        if g.graph is None:
+            self._capture(g)
+        g.graph.replay()
+        rows = [b for b in range(B) for _ in want[b]]
+        if rows == list(range(B)):
+            return g.logits[:B]
+        if not rows:
+            return g.logits[:0]
+        return g.logits[torch.tensor(rows, device=self.device)]
+
+    def _capture(self, g: _DecodeGraph) -> None:
+        q_lens = [1] * g.n_pad
+        kv_bound = g.table_width * PAGE
+
+        def run():
+            batch = StepBatch(g.layout, g.buffer, q_lens=q_lens, starts=[0] * g.n_pad)
+            batch.workspace = self.workspace
+            batch.kv_bound = kv_bound
+            return self.model.forward(batch, self.cache)
+
+        # Warm-up outside capture (compiles/loads kernels, grows scratch buffers).
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            run()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        self.workspace.frozen = True
+        try:
+            with torch.cuda.graph(graph):
+                g.logits = run()
+        finally:
+            self.workspace.frozen = False
+        # The graph holds raw pointers into the scratch buffers: keep those alive
+        # even if the workspace later replaces them by larger ones.
+        g.keepalive = dict(self.workspace.buffers)
+        g.graph = graph

@@ -1,0 +1,106 @@
+"""A model built from a :class:`ModelSpec`: parts, their tensors, one forward pass.
+
+The class is the same for every architecture: it builds each layer's parts from
+the spec through the part registry, knows every tensor's full name (the part's
+local name behind the prefixes the spec gives), and runs the layers in the
+order of the spec's schedule over one :class:`StepBatch`.
+"""
+from __future__ import annotations
+
+import fnmatch
+from typing import Callable, Dict, List, Optional, Tuple
+
+import torch
+
+from ..parts.base import Block, BuildContext, CacheNeed, Hidden, Part, TensorSpec, build_part
+from ..parts import standard as _standard_parts   # registers the standard kinds  # noqa: F401
+from .spec import ModelSpec
+
+
+class Model:
+    def __init__(self, spec: ModelSpec, dtype: torch.dtype, device: torch.device | str):
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"compute dtype {dtype} is not built (bfloat16 or float32)")
+        spec.validate()
+        self.spec = spec
+        self.ctx = BuildContext(dtype=dtype, device=torch.device(device))
+        ctx = self.ctx
+        self.embedding = build_part("embedding", spec.embedding, ctx)
+        self.blocks: List[Block] = []
+        for ls in spec.layers:
+            mixer = build_part("mixer", ls.mixer, ctx)
+            mixer_norm = build_part("norm", ls.mixer_norm, ctx)
+            ffn = build_part("ffn", ls.ffn, ctx)
+            ffn_norm = build_part("norm", ls.ffn_norm, ctx)
+            self.blocks.append(build_part("block", ls.block, ctx, mixer, mixer_norm, ffn, ffn_norm))
+        self.final_norm = build_part("norm", spec.final_norm, ctx)
+        self.head = build_part("head", spec.head, ctx)
+        self.loaded = False
+
+    # ---- tensors ---------------------------------------------------------
+    def _places(self) -> List[Tuple[str, Part]]:
+        s = self.spec
+        out: List[Tuple[str, Part]] = [(s.embedding_prefix, self.embedding)]
+        for ls, blk in zip(s.layers, self.blocks):
+            out += [(ls.prefix + ls.names["mixer_norm"], blk.mixer_norm),
+                    (ls.prefix + ls.names["mixer"], blk.mixer),
+                    (ls.prefix + ls.names["ffn_norm"], blk.ffn_norm),
+                    (ls.prefix + ls.names["ffn"], blk.ffn)]
+        out += [(s.final_norm_prefix, self.final_norm), (s.head_prefix, self.head)]
+        return out
+
+    def tensor_table(self) -> Dict[str, TensorSpec]:
+        """Full tensor name -> what is expected under it."""
+        table: Dict[str, TensorSpec] = {}
+        for prefix, part in self._places():
+            for ts in part.tensor_specs():
+                table[prefix + ts.name] = ts
+        return table
+
+    def is_ignored(self, name: str) -> bool:
+        return any(fnmatch.fnmatchcase(name, pat) for pat in self.spec.ignore_tensors)
+
+    def load(self, get: Callable[[str], Optional[torch.Tensor]]) -> None:
+        """``get(full_name)`` returns a tensor (any device) or None."""
+        for prefix, part in self._places():
+            fetch = (lambda p: (lambda local: get(p + local)))(prefix)
+            if part is self.head:
+                part.load(fetch, self.embedding)
+            else:
+                part.load(fetch)
+        self.loaded = True
+
+    # ---- sizes -------------------------------------------------------------
+    def cache_needs(self) -> List[Optional[CacheNeed]]:
+        """For each schedule entry, the cache storage it owns (None if it reads
+        another entry's or its mixer keeps nothing)."""
+        needs: List[Optional[CacheNeed]] = []
+        for e in self.spec.schedule:
+            needs.append(None if e.read_cache_of is not None else self.blocks[e.layer].mixer.cache_need())
+        return needs
+
+    def weight_bytes_per_step(self) -> int:
+        """Bytes of weights one step reads (each schedule entry reads its layer's)."""
+        n = self.final_norm.weight_bytes() + self.head.weight_bytes()
+        for e in self.spec.schedule:
+            b = self.blocks[e.layer]
+            n += b.mixer.weight_bytes() + b.ffn.weight_bytes() + b.mixer_norm.weight_bytes() + b.ffn_norm.weight_bytes()
+        return n
+
+    # ---- forward -------------------------------------------------------------
+    def forward(self, batch, cache) -> torch.Tensor:
+        """Run the batch's tokens through every scheduled layer, appending to the
+        cache, and return float32 logits [len(batch.want), vocab]."""
+        if not self.loaded:
+            raise RuntimeError("the model has no weights yet")
+        h = Hidden(self.embedding.forward(batch.tokens))
+        for i, e in enumerate(self.spec.schedule):
+            src = i if e.read_cache_of is None else e.read_cache_of
+            h = self.blocks[e.layer].forward(h, batch, cache.view(src, batch), e.read_cache_of is None)
+        if batch.n_want == 0:
+            return torch.empty((0, self.spec.vocab), dtype=torch.float32, device=self.ctx.device)
+        if h.pending is not None:
+            xn = self.final_norm.add_forward(h.x, h.pending, self.ctx.dtype, batch.want)
+        else:
+            xn = self.final_norm.forward(h.x, self.ctx.dtype, batch.want)
+        return self.head.forward(xn)

@@ -1,0 +1,350 @@
+"""The kernels, as Python functions over CUDA tensors.
+
+Every function checks its arguments (device, dtype, shape, contiguity), passes
+raw pointers and the current CUDA stream to an exported C function of one of
+the libraries built from ``wick_b200/csrc``, and raises :class:`KernelError`
+with the library's message if the call is refused.  There is no fallback of
+any kind: without a CUDA device or without ``nvcc`` these functions raise.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from .build import BuildError, load_library
+
+PAGE = 64
+DECODE_SPLIT = 256
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_CT = {"p": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_int64, "f": ctypes.c_float}
+
+# Argument kinds of an exported function: p pointer, i int32, l int64, f float; the
+# last pointer is always the stream.
+
+
+def _dt(t: torch.Tensor) -> str:
+    if t.dtype == torch.bfloat16:
+        return "bf16"
+    if t.dtype == torch.float32:
+        return "f32"
+    raise KernelError(f"unsupported element type {t.dtype} (bfloat16 and float32 are built)")
+
+
+class _Lib:
+    """A loaded library with lazily configured functions."""
+
+    def __init__(self, name, sources, defines=()):
+        self._lib = load_library(name, sources, defines)
+        self._fns: Dict[str, object] = {}
+
+    def fn(self, name: str, sig: str):
+        f = self._fns.get(name)
+        if f is None:
+            try:
+                f = getattr(self._lib, name)
+            except AttributeError:
+                raise KernelError(f"{name} is not exported by {self._lib._name}") from None
+            f.argtypes = [_CT[c] for c in sig]
+            f.restype = ctypes.c_int
+            self._fns[name] = f
+        return f
+
+    def call(self, name: str, sig: str, *args):
+        rc = self.fn(name, sig)(*args)
+        if rc != 0:
+            raise KernelError(self._lib.wick_last_error().decode("utf-8", "replace"))
+
+
+_libs: Dict[str, _Lib] = {}
+
+
+def _core() -> _Lib:
+    lib = _libs.get("core")
+    if lib is None:
+        lib = _libs["core"] = _Lib("wick_core", ["core.cu", "sample.cu"])
+    return lib
+
+
+def _simt() -> _Lib:
+    lib = _libs.get("simt")
+    if lib is None:
+        lib = _libs["simt"] = _Lib("wick_gemm_simt", ["gemm_simt.cu"])
+    return lib
+
+
+def _attn(head_dim: int) -> _Lib:
+    key = f"attn{head_dim}"
+    lib = _libs.get(key)
+    if lib is None:
+        if head_dim % 16 != 0 or not 16 <= head_dim <= 256:
+            raise KernelError(f"attention kernels take a head_dim that is a multiple of 16 between 16 and 256, "
+                              f"not {head_dim}")
+        lib = _libs[key] = _Lib(f"wick_attn_hd{head_dim}", ["attn.cu"], [f"WICK_HD={head_dim}"])
+    return lib
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need(cond: bool, msg: str) -> None:
+    if not cond:
+        raise KernelError(msg)
+
+
+def _cuda(name: str, t: torch.Tensor, dtype=None, shape=None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (the kernels have no CPU form)")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, is {t.dtype}")
+    if shape is not None and tuple(t.shape) != tuple(shape):
+        raise KernelError(f"{name} must have shape {tuple(shape)}, has {tuple(t.shape)}")
+
+
+# ---------------------------------------------------------------------------
+def embed(table: torch.Tensor, tokens: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """float32 [n, width] rows of ``table`` [vocab, width] at int32 ``tokens`` [n]."""
+    _cuda("table", table)
+    _cuda("tokens", tokens, torch.int32)
+    n, (vocab, width) = tokens.numel(), table.shape
+    if out is None:
+        out = torch.empty((n, width), dtype=torch.float32, device=table.device)
+    _cuda("out", out, torch.float32, (n, width))
+    _core().call(f"wick_embed_{_dt(table)}", "pppiilp", _p(table), _p(tokens), _p(out), n, width, vocab, _stream())
+    return out
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype, *,
+            delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
+            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """RMS norm of float32 ``x`` [n, width] into ``out_dtype``.
+
+    delta: float32 [splits, n, width]; added to ``x`` in place (for the rows that
+    are normalised) before the norm.  rows: int32 indices; only those rows are
+    normalised (and updated), the result has len(rows) rows."""
+    _cuda("x", x, torch.float32)
+    n, width = x.shape
+    _cuda("weight", weight, torch.float32, (width,))
+    splits = 0
+    if delta is not None:
+        _cuda("delta", delta, torch.float32)
+        _need(delta.dim() == 3 and tuple(delta.shape[1:]) == (n, width),
+              f"delta must be [splits, {n}, {width}], is {tuple(delta.shape)}")
+        splits = delta.shape[0]
+    if rows is not None:
+        _cuda("rows", rows, torch.int32)
+    n_out = n if rows is None else rows.numel()
+    if out is None:
+        out = torch.empty((n_out, width), dtype=out_dtype, device=x.device)
+    _cuda("out", out, out_dtype, (n_out, width))
+    _core().call(f"wick_rmsnorm_{_dt(out)}", "ppilpfppiip", _p(x), _p(delta), splits, n, _p(weight), float(eps),
+                 _p(rows), _p(out), n_out, width, _stream())
+    return out
+
+
+def add_delta(x: torch.Tensor, delta: torch.Tensor) -> torch.Tensor:
+    """x += delta[0] + delta[1] + ... in place (float32)."""
+    _cuda("x", x, torch.float32)
+    _cuda("delta", delta, torch.float32)
+    _need(delta.dim() == 3 and tuple(delta.shape[1:]) == tuple(x.shape), "delta must be [splits, *x.shape]")
+    _core().call("wick_add_delta", "ppilp", _p(x), _p(delta), delta.shape[0], x.numel(), _stream())
+    return x
+
+
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """cos and sin of ``positions[t] * inv_freq[i]`` (float32 product), each [n, half]."""
+    _cuda("positions", positions, torch.int32)
+    _cuda("inv_freq", inv_freq, torch.float32)
+    n, half = positions.numel(), inv_freq.numel()
+    cos = torch.empty((n, half), dtype=torch.float32, device=positions.device)
+    sin = torch.empty_like(cos)
+    _core().call("wick_rope_table", "ppppiip", _p(positions), _p(inv_freq), _p(cos), _p(sin), n, half, _stream())
+    return cos, sin
+
+
+def qk_norm_rope_append(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, *,
+                        q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                        cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], kv: Optional[torch.Tensor],
+                        page_table: torch.Tensor, seq_of_token: torch.Tensor, positions: torch.Tensor,
+                        write_kv: bool = True, q_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Per-head RMS norm of q and k (if weights are given), half-split rotation
+    (if tables are given), then q -> ``q_out`` [n, n_heads, head_dim] and k, v ->
+    the cache ``kv`` [pages, 2, n_kv, 64, head_dim] at each token's position."""
+    _cuda("qkv", qkv)
+    n = qkv.shape[0]
+    _need(qkv.dim() == 2 and qkv.shape[1] == (n_heads + 2 * n_kv) * head_dim,
+          f"qkv must be [n, {(n_heads + 2 * n_kv) * head_dim}], is {tuple(qkv.shape)}")
+    for nm, w in (("q_weight", q_weight), ("k_weight", k_weight)):
+        if w is not None:
+            _cuda(nm, w, torch.float32, (head_dim,))
+    _need((q_weight is None) == (k_weight is None), "q and k norm weights come together")
+    if cos is not None:
+        _cuda("cos", cos, torch.float32, (n, head_dim // 2))
+        _cuda("sin", sin, torch.float32, (n, head_dim // 2))
+    if write_kv:
+        _cuda("kv", kv, qkv.dtype)
+        _need(kv.dim() == 5 and tuple(kv.shape[1:]) == (2, n_kv, PAGE, head_dim),
+              f"kv must be [pages, 2, {n_kv}, {PAGE}, {head_dim}], is {tuple(kv.shape)}")
+    _cuda("page_table", page_table, torch.int32)
+    _cuda("seq_of_token", seq_of_token, torch.int32, (n,))
+    _cuda("positions", positions, torch.int32, (n,))
+    if q_out is None:
+        q_out = torch.empty((n, n_heads, head_dim), dtype=qkv.dtype, device=qkv.device)
+    _cuda("q_out", q_out, qkv.dtype, (n, n_heads, head_dim))
+    _core().call(f"wick_qk_norm_rope_append_{_dt(qkv)}", "piiiippfpppppippip",
+                 _p(qkv), n, n_heads, n_kv, head_dim, _p(q_weight), _p(k_weight), float(eps), _p(cos), _p(sin),
+                 _p(q_out), _p(kv) if write_kv else None, _p(page_table), page_table.shape[-1], _p(seq_of_token),
+                 _p(positions), 1 if write_kv else 0, _stream())
+    return q_out
+
+
+def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    _cuda("gate", gate)
+    _cuda("up", up, gate.dtype, gate.shape)
+    out = torch.empty_like(gate)
+    _core().call(f"wick_silu_mul_{_dt(gate)}", "ppplp", _p(gate), _p(up), _p(out), gate.numel(), _stream())
+    return out
+
+
+# ---------------------------------------------------------------------------
+def gemm_simt(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, *, gated: bool = False,
+              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x [m, k] times w [n, k] transposed on the CUDA cores, float32 accumulation.
+    gated: w is [2n, k] (gate rows, then up rows); returns silu(x gate^T) * (x up^T)."""
+    _cuda("x", x)
+    _cuda("w", w, x.dtype)
+    m, k = x.shape
+    _need(w.dim() == 2 and w.shape[1] == k, f"w must be [n, {k}], is {tuple(w.shape)}")
+    n = w.shape[0] // 2 if gated else w.shape[0]
+    if gated:
+        _need(w.shape[0] % 2 == 0, "gated weight needs an even number of rows")
+    if out is None:
+        out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    _cuda("out", out, out_dtype, (m, n))
+    name = f"wick_gemm_simt_{_dt(x)}_{_dt(out)}" + ("_gated" if gated else "")
+    if name not in ("wick_gemm_simt_bf16_bf16", "wick_gemm_simt_bf16_f32", "wick_gemm_simt_f32_f32",
+                    "wick_gemm_simt_bf16_bf16_gated", "wick_gemm_simt_f32_f32_gated"):
+        raise KernelError(f"no matrix product from {x.dtype} to {out_dtype}" + (" (gated)" if gated else ""))
+    _simt().call(name, "pppiiip", _p(x), _p(w), _p(out), m, n, k, _stream())
+    return out
+
+
+# ---------------------------------------------------------------------------
+def attention_prompt(q: torch.Tensor, kv: torch.Tensor, batch, scale: float,
+                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention of the step's new tokens over the cache (which already
+    holds their keys and values).  q: [n, heads, d]; kv: [pages, 2, kv_heads, 64, d]."""
+    _cuda("q", q)
+    n, n_heads, hd = q.shape
+    _cuda("kv", kv, q.dtype)
+    _need(kv.dim() == 5 and kv.shape[1] == 2 and kv.shape[3] == PAGE and kv.shape[4] == hd,
+          f"kv must be [pages, 2, kv_heads, {PAGE}, {hd}], is {tuple(kv.shape)}")
+    n_kv = kv.shape[2]
+    _need(n == batch.n_tokens, f"q has {n} rows, the batch {batch.n_tokens} tokens")
+    if out is None:
+        out = torch.empty_like(q)
+    _cuda("out", out, q.dtype, q.shape)
+    _attn(hd).call(f"wick_attn_prompt_{_dt(q)}", "pppppipppiiifp", _p(q), _p(kv), _p(out), _p(batch.tile_seq),
+                   _p(batch.tile_q0), batch.n_tiles, _p(batch.cu_seqlens), _p(batch.start), _p(batch.page_table),
+                   batch.table_width, n_heads, n_kv, float(scale), _stream())
+    return out
+
+
+def attention_decode_scratch_floats(n_seqs: int, n_heads: int, head_dim: int, max_kv_len: int) -> int:
+    return n_seqs * n_heads * max(1, -(-max_kv_len // DECODE_SPLIT)) * (head_dim + 2)
+
+
+def attention_decode(q: torch.Tensor, kv: torch.Tensor, batch, scale: float, scratch: torch.Tensor,
+                     out: Optional[torch.Tensor] = None, max_kv_len: Optional[int] = None) -> torch.Tensor:
+    """One new token per sequence.  scratch: float32, at least
+    :func:`attention_decode_scratch_floats` elements; it holds the per-split
+    partial sums between the two kernels."""
+    _cuda("q", q)
+    n, n_heads, hd = q.shape
+    _cuda("kv", kv, q.dtype)
+    _need(kv.dim() == 5 and kv.shape[1] == 2 and kv.shape[3] == PAGE and kv.shape[4] == hd,
+          f"kv must be [pages, 2, kv_heads, {PAGE}, {hd}], is {tuple(kv.shape)}")
+    n_kv = kv.shape[2]
+    _need(n == batch.n_seqs, f"decode attention takes one token per sequence: {n} rows, {batch.n_seqs} sequences")
+    _cuda("scratch", scratch, torch.float32)
+    if out is None:
+        out = torch.empty_like(q)
+    _cuda("out", out, q.dtype, q.shape)
+    mk = batch.max_kv_len if max_kv_len is None else max_kv_len
+    _attn(hd).call(f"wick_attn_decode_{_dt(q)}", "pppplpiipiiifp", _p(q), _p(kv), _p(out),
+                   _p(scratch), scratch.numel(), _p(batch.kv_len), n, mk, _p(batch.page_table), batch.table_width,
+                   n_heads, n_kv, float(scale), _stream())
+    return out
+
+
+# ---------------------------------------------------------------------------
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """First index of each row's maximum (int32 [rows])."""
+    _cuda("logits", logits, torch.float32)
+    rows, vocab = logits.shape
+    if out is None:
+        out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    _cuda("out", out, torch.int32, (rows,))
+    _core().call("wick_argmax", "ppiip", _p(logits), _p(out), rows, vocab, _stream())
+    return out
+
+
+def sample_temperature(logits: torch.Tensor, temperature: float, uniforms: torch.Tensor,
+                       out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One draw per row from softmax(logits / temperature): the first index whose
+    cumulative probability (in index order) reaches uniforms[row] times the total."""
+    _cuda("logits", logits, torch.float32)
+    rows, vocab = logits.shape
+    _cuda("uniforms", uniforms, torch.float32, (rows,))
+    _need(temperature > 0, "temperature must be positive (0 means greedy: use argmax)")
+    if out is None:
+        out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    _cuda("out", out, torch.int32, (rows,))
+    _core().call("wick_sample_temperature", "pppiifp", _p(logits), _p(uniforms), _p(out), rows, vocab,
+                 float(1.0 / temperature), _stream())
+    return out
+
+
+def top_k(logits: torch.Tensor, k: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The k largest entries of each row, sorted by value (descending), ties by
+    index (ascending): (float32 [rows, k], int32 [rows, k])."""
+    _cuda("logits", logits, torch.float32)
+    rows, vocab = logits.shape
+    _need(1 <= k <= min(vocab, 1024), f"top_k on the device takes 1 <= k <= min(vocab, 1024), not {k}")
+    vals = torch.empty((rows, k), dtype=torch.float32, device=logits.device)
+    idx = torch.empty((rows, k), dtype=torch.int32, device=logits.device)
+    _core().call("wick_top_k", "pppiiip", _p(logits), _p(vals), _p(idx), rows, vocab, k, _stream())
+    return vals, idx
+
+
+def repetition_penalty(logits: torch.Tensor, histories, penalty: float) -> torch.Tensor:
+    """In place: every distinct token of histories[row] has its logit divided by
+    ``penalty`` if positive, multiplied otherwise."""
+    _cuda("logits", logits, torch.float32)
+    rows, vocab = logits.shape
+    _need(len(histories) == rows, "one history per row")
+    r, t = [], []
+    for i, h in enumerate(histories):
+        d = sorted(set(int(x) for x in h))
+        r += [i] * len(d)
+        t += d
+    if not t:
+        return logits
+    dev = torch.tensor([r, t], dtype=torch.int32).to(logits.device)
+    _core().call("wick_repetition_penalty", "pppiifp", _p(logits), _p(dev[0]), _p(dev[1]), len(t), vocab,
+                 float(penalty), _stream())
+    return logits

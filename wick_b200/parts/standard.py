@@ -1,0 +1,287 @@
+"""The parts the Qwen3 dense decoder is put together from.
+
+Each class takes its sizes and constants from ``params`` and nothing else:
+
+=============  ======================  ==========================================
+category       kind                    params
+=============  ======================  ==========================================
+norm           ``rms``                 width, eps
+position       ``rotary_half_split``   head_dim, theta
+position       ``none``                —
+mixer          ``gqa_attention``       width, heads, kv_heads, head_dim,
+                                       qk_norm (PartSpec or None),
+                                       position (PartSpec), scale (or None)
+ffn            ``gated_mlp``           width, intermediate, activation ("silu")
+block          ``prenorm_residual``    —
+embedding      ``table``               vocab, width
+head           ``linear``              vocab, width, tied
+=============  ======================  ==========================================
+
+Formulas and their place in wick: RMS norm ``src/kernels.rs:343-357``; rotation
+``src/model.rs:404-414`` with ``inv_freq`` from ``src/config.rs:162-167``;
+attention ``src/model.rs:452-487,520-553``; SwiGLU MLP ``src/model.rs:490-503``;
+output head ``src/model.rs:508-515`` with the tie rule of ``src/model.rs:190``.
+"""
+from __future__ import annotations
+
+import math
+from typing import Any, List, Mapping, Optional
+
+import torch
+
+from .. import ops
+from ..models.spec import PartSpec
+from .base import (Block, BuildContext, CacheNeed, Embedding, FeedForward, Fetch, Head, Hidden, Mixer,
+                   Norm, Part, Position, TensorSpec, as_splits, build_part, register_part)
+from .linear import Linear
+
+
+# ---------------------------------------------------------------------------
+class RMSNorm(Norm):
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.width = int(params["width"])
+        self.eps = float(params["eps"])
+        self.weight: Optional[torch.Tensor] = None
+
+    def tensor_specs(self):
+        return [TensorSpec("weight", (self.width,), "vector")]
+
+    def load(self, fetch):
+        self.weight = self.ctx.hold(fetch("weight"), "vector")
+
+    def forward(self, x, out_dtype, rows=None):
+        return ops.rmsnorm(x, self.weight, self.eps, out_dtype, rows=rows)
+
+    def add_forward(self, x, delta, out_dtype, rows=None):
+        return ops.rmsnorm(x, self.weight, self.eps, out_dtype, delta=delta, rows=rows)
+
+    def weight_bytes(self):
+        return self.width * 4
+
+
+# ---------------------------------------------------------------------------
+class RotaryHalfSplit(Position):
+    """Whole-head rotation of the pairs (i, i + head_dim/2) by the angle
+    ``position * inv_freq[i]`` with ``inv_freq[i] = theta ** (-2i / head_dim)``,
+    evaluated in float64 and rounded to float32 once."""
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.head_dim = int(params["head_dim"])
+        self.theta = float(params["theta"])
+        d = self.head_dim
+        inv = [1.0 / (self.theta ** (2.0 * i / d)) for i in range(d // 2)]
+        self.inv_freq = torch.tensor(inv, dtype=torch.float64).to(torch.float32).to(ctx.device)
+
+    def rotary_inv_freq(self):
+        return self.inv_freq
+
+    def tables(self, batch):
+        """cos/sin [tokens, head_dim/2] of this step, computed once and shared by
+        every layer that uses an equal encoding."""
+        key = ("rotary_half_split", self.head_dim, self.theta)
+        t = batch.memo.get(key)
+        if t is None:
+            t = batch.memo[key] = ops.rope_table(batch.positions, self.inv_freq)
+        return t
+
+
+class NoPosition(Position):
+    def rotary_inv_freq(self):
+        return None
+
+    def apply(self, q, k, positions):
+        return None
+
+
+# ---------------------------------------------------------------------------
+class GQAttention(Mixer):
+    """Causal attention with grouped key/value heads over a paged cache.
+
+    q, k, v = x Wq^T, x Wk^T, x Wv^T (no bias); optional per-head norm of q and k
+    (one weight vector shared by all heads) before the position encoding; k and v
+    are appended to the cache; every new token attends to positions 0..its own;
+    the result goes through Wo.  The three projections are held as one matrix.
+    """
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        p = params
+        self.width, self.heads, self.kv_heads, self.head_dim = (int(p["width"]), int(p["heads"]),
+                                                                int(p["kv_heads"]), int(p["head_dim"]))
+        if self.heads % self.kv_heads != 0:
+            raise ValueError("heads must be a multiple of kv_heads")
+        if self.head_dim % 16 != 0 or not 16 <= self.head_dim <= 256:
+            raise ValueError(f"the attention kernels take a head_dim that is a multiple of 16 between 16 and 256, "
+                             f"not {self.head_dim}")
+        self.q_dim, self.kv_dim = self.heads * self.head_dim, self.kv_heads * self.head_dim
+        self.scale = float(p["scale"]) if p.get("scale") is not None else 1.0 / math.sqrt(self.head_dim)
+        self.window = p.get("window")
+        if self.window is not None:
+            raise ValueError("windowed attention is not built")
+        qk = p.get("qk_norm")
+        self.q_norm = build_part("norm", qk, ctx) if qk is not None else None
+        self.k_norm = build_part("norm", qk, ctx) if qk is not None else None
+        if qk is not None and not isinstance(self.q_norm, RMSNorm):
+            raise ValueError("the fused q/k norm kernel is an RMS norm; another norm needs its own kernel")
+        self.position = build_part("position", p.get("position") or PartSpec("none"), ctx)
+        self.qkv = Linear(self.q_dim + 2 * self.kv_dim, self.width, ctx)
+        self.o = Linear(self.width, self.q_dim, ctx)
+
+    def tensor_specs(self):
+        specs = [TensorSpec("q_proj.weight", (self.q_dim, self.width)),
+                 TensorSpec("k_proj.weight", (self.kv_dim, self.width)),
+                 TensorSpec("v_proj.weight", (self.kv_dim, self.width)),
+                 TensorSpec("o_proj.weight", (self.width, self.q_dim))]
+        if self.q_norm is not None:
+            specs += [TensorSpec("q_norm." + s.name, s.shape, s.role) for s in self.q_norm.tensor_specs()]
+            specs += [TensorSpec("k_norm." + s.name, s.shape, s.role) for s in self.k_norm.tensor_specs()]
+        return specs
+
+    def load(self, fetch):
+        self.qkv.load_rows([fetch("q_proj.weight"), fetch("k_proj.weight"), fetch("v_proj.weight")])
+        self.o.load_rows([fetch("o_proj.weight")])
+        if self.q_norm is not None:
+            self.q_norm.load(lambda n: fetch("q_norm." + n))
+            self.k_norm.load(lambda n: fetch("k_norm." + n))
+
+    def cache_need(self):
+        return CacheNeed("paged_kv", kv_heads=self.kv_heads, head_dim=self.head_dim, window=self.window)
+
+    def weight_bytes(self):
+        return self.qkv.weight_bytes() + self.o.weight_bytes() + (2 * self.head_dim * 4 if self.q_norm else 0)
+
+    def forward(self, x, batch, cache, write_cache):
+        qkv = self.qkv.forward(x, self.ctx.dtype)                       # [n, q_dim + 2 kv_dim]
+        inv_freq = self.position.rotary_inv_freq()
+        cos = sin = None
+        if inv_freq is not None:
+            cos, sin = self.position.tables(batch)
+        q = ops.qk_norm_rope_append(
+            qkv, self.heads, self.kv_heads, self.head_dim,
+            q_weight=self.q_norm.weight if self.q_norm else None,
+            k_weight=self.k_norm.weight if self.k_norm else None,
+            eps=self.q_norm.eps if self.q_norm else 0.0,
+            cos=cos, sin=sin, kv=cache.kv, page_table=batch.page_table,
+            seq_of_token=batch.seq_of_token, positions=batch.positions, write_kv=write_cache)
+        if inv_freq is None and not isinstance(self.position, NoPosition):
+            raise NotImplementedError("a position encoding that is not a half-split rotation has to be applied "
+                                      "before the cache append; give the mixer a kernel for it")
+        if batch.is_decode:
+            need = ops.attention_decode_scratch_floats(batch.n_seqs, self.heads, self.head_dim, batch.kv_bound)
+            att = ops.attention_decode(q, cache.kv, batch, self.scale,
+                                       batch.workspace.get("attention_decode", need, torch.float32),
+                                       max_kv_len=batch.kv_bound)
+        else:
+            att = ops.attention_prompt(q, cache.kv, batch, self.scale)
+        return self.o.forward_delta(att.view(batch.n_tokens, self.q_dim))
+
+
+# ---------------------------------------------------------------------------
+class GatedMLP(FeedForward):
+    """down( act(x gate^T) * (x up^T) ), no biases; gate and up are one matrix."""
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.width, self.intermediate = int(params["width"]), int(params["intermediate"])
+        act = params.get("activation", "silu")
+        if act != "silu":
+            raise ValueError(f"unsupported activation {act}")
+        self.gate_up = Linear(2 * self.intermediate, self.width, ctx, gated=True)
+        self.down = Linear(self.width, self.intermediate, ctx)
+
+    def tensor_specs(self):
+        return [TensorSpec("gate_proj.weight", (self.intermediate, self.width)),
+                TensorSpec("up_proj.weight", (self.intermediate, self.width)),
+                TensorSpec("down_proj.weight", (self.width, self.intermediate))]
+
+    def load(self, fetch):
+        self.gate_up.load_rows([fetch("gate_proj.weight"), fetch("up_proj.weight")])
+        self.down.load_rows([fetch("down_proj.weight")])
+
+    def weight_bytes(self):
+        return self.gate_up.weight_bytes() + self.down.weight_bytes()
+
+    def forward(self, x, batch):
+        act = self.gate_up.forward(x, self.ctx.dtype)                   # [n, intermediate]
+        return self.down.forward_delta(act)
+
+
+# ---------------------------------------------------------------------------
+class PreNormResidual(Block):
+    """x += mixer(norm1(x)); x += ffn(norm2(x)) — each addition is left pending
+    so that the following norm's kernel performs it."""
+
+    def forward(self, h, batch, cache, write_cache):
+        dt = self.ctx.dtype
+        if h.pending is not None:
+            xn = self.mixer_norm.add_forward(h.x, h.pending, dt)
+        else:
+            xn = self.mixer_norm.forward(h.x, dt)
+        d = as_splits(self.mixer.forward(xn, batch, cache, write_cache))
+        xn = self.ffn_norm.add_forward(h.x, d, dt)
+        h.pending = as_splits(self.ffn.forward(xn, batch))
+        return h
+
+
+# ---------------------------------------------------------------------------
+class TableEmbedding(Embedding):
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.vocab, self.width = int(params["vocab"]), int(params["width"])
+        self.weight: Optional[torch.Tensor] = None
+
+    def tensor_specs(self):
+        return [TensorSpec("weight", (self.vocab, self.width))]
+
+    def load(self, fetch):
+        self.weight = self.ctx.hold(fetch("weight"), "matrix")
+
+    def forward(self, tokens):
+        return ops.embed(self.weight, tokens)
+
+    def weight_bytes(self):
+        return 0            # a step reads one row per token, not the table
+
+
+class LinearHead(Head):
+    """logits = x W^T in float32.  ``tied``: W is the embedding table.  As in wick
+    (model.rs:190) the head is also tied when its own tensor is absent."""
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.vocab, self.width = int(params["vocab"]), int(params["width"])
+        self.tied = bool(params.get("tied", False))
+        self.linear = Linear(self.vocab, self.width, ctx)
+        self.is_tied = self.tied
+
+    def tensor_specs(self):
+        return [TensorSpec("weight", (self.vocab, self.width), optional=True)]
+
+    def load(self, fetch, embedding: Optional[TableEmbedding] = None):
+        w = None if self.tied else fetch("weight")
+        if w is None:
+            if embedding is None or embedding.weight is None:
+                raise ValueError("a tied head needs the embedding table")
+            self.linear.use(embedding.weight)
+            self.is_tied = True
+        else:
+            self.linear.load_rows([w])
+            self.is_tied = False
+
+    def forward(self, x):
+        return self.linear.forward(x, torch.float32)
+
+    def weight_bytes(self):
+        return self.linear.weight_bytes()
+
+
+register_part("norm", "rms", RMSNorm)
+register_part("position", "rotary_half_split", RotaryHalfSplit)
+register_part("position", "none", NoPosition)
+register_part("mixer", "gqa_attention", GQAttention)
+register_part("ffn", "gated_mlp", GatedMLP)
+register_part("block", "prenorm_residual", PreNormResidual)
+register_part("embedding", "table", TableEmbedding)
+register_part("head", "linear", LinearHead)
