@@ -396,7 +396,6 @@ int attn_decode(const void* q, const void* kv, void* out, float* part_o, float* 
 using namespace wick;
 typedef __nv_bfloat16 bf16;
 
-WICK_API const char* wick_last_error() { return error_buffer(); }
 WICK_API int wick_attn_head_dim() { return HD; }
 WICK_API int wick_attn_decode_split() { return SPLIT; }
 

@@ -129,3 +129,6 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 inline int ceil_div(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }
 
 }  // namespace wick
+
+// The message of the last failed call of this library on this thread.
+extern "C" __attribute__((visibility("default"), weak)) const char* wick_last_error() { return wick::error_buffer(); }

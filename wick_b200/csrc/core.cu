@@ -185,7 +185,6 @@ int rmsnorm(float* x, const float* delta, int splits, int64_t n_rows_x, const fl
 using namespace wick;
 typedef __nv_bfloat16 bf16;
 
-WICK_API const char* wick_last_error() { return error_buffer(); }
 
 WICK_API int wick_embed_bf16(const void* table, const int* tokens, float* out, int n, int width, int64_t vocab, void* s) {
     return embed<bf16>(table, tokens, out, n, width, vocab, (cudaStream_t)s);
