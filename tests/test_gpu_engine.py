@@ -1,0 +1,218 @@
+"""The engine against the plain implementation, in float32 and bfloat16: each
+request alone and whole; the last 32 tokens one by one; batches of unequal
+lengths whose shorter requests end earlier, one batch after another so that
+slots and pages are used again; long decoding; the first tokens of a sequence;
+uneven chunks; captured and eager decode steps."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+import wick_b200 as wick  # noqa: E402
+from helpers import (CONFIGS, assert_logits_close, make_engine, plain_logits, poison_all,  # noqa: E402
+                     poison_free_pages, random_tokens)
+
+DTYPES = ["float32", "bfloat16"]
+NAMES = ["A", "B"]
+
+
+def vocab_of(name):
+    return CONFIGS[name]["vocab_size"]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES + ["C"])
+def test_each_request_alone_and_whole(name, dtype):
+    eng = make_engine(name, dtype)
+    poison_all(eng)
+    for n, seed in ((1, 1), (5, 2), (64, 3), (65, 4), (200, 5)):
+        toks = random_tokens(vocab_of(name), n, seed)
+        s = eng.open_seq()
+        got = eng.step([s], [toks], [list(range(n))])
+        eng.close_seq(s)
+        assert_logits_close(got, plain_logits(name, toks), dtype, f"{name} whole n={n}")
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_last_32_tokens_one_by_one(name, dtype, graphs):
+    eng = make_engine(name, dtype, use_graphs=graphs)
+    poison_all(eng)
+    toks = random_tokens(vocab_of(name), 150, 11)
+    ref = plain_logits(name, toks)
+    s = eng.open_seq()
+    head = len(toks) - 32
+    got = [eng.step([s], [toks[:head]], [list(range(head))]).clone()]
+    for i in range(head, len(toks)):
+        got.append(eng.step([s], [[toks[i]]]).clone())
+    eng.close_seq(s)
+    assert_logits_close(torch.cat(got), ref, dtype, f"{name} decode of the last 32")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_uneven_chunks_match_one_pass(name, dtype):
+    # wick tests/tiny_models.rs:73-95
+    eng = make_engine(name, dtype)
+    poison_all(eng)
+    toks = random_tokens(vocab_of(name), 48, 12)
+    ref = plain_logits(name, toks)
+    s = eng.open_seq()
+    pos, got = 0, []
+    for size in [1, 5, 2, 7, 1, 1, 13, 3, 15]:
+        got.append(eng.step([s], [toks[pos:pos + size]], [list(range(size))]).clone())
+        pos += size
+    eng.close_seq(s)
+    assert pos == len(toks)
+    assert_logits_close(torch.cat(got), ref, dtype, f"{name} uneven chunks")
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_unequal_batches_one_after_another_reuse_slots(name, dtype, graphs):
+    """Three batches through a cache that holds only one of them at a time.
+    Every request runs prompt-then-decode; shorter requests end earlier and the
+    batch shrinks; freed pages are filled with NaN before the next batch starts."""
+    lens_per_batch = [(5, 11, 17, 70), (1, 7, 30, 64), (33, 2, 129)]
+    dec = {0: 3, 1: 9, 2: 5, 3: 12}
+    eng = make_engine(name, dtype, max_tokens=64 * 8, use_graphs=graphs)
+    poison_all(eng)
+    seed = 100
+    for lens in lens_per_batch:
+        seqs = []
+        for i, n in enumerate(lens):
+            seed += 1
+            seqs.append(random_tokens(vocab_of(name), n + dec[i], seed))
+        refs = [plain_logits(name, s) for s in seqs]
+        slots = [eng.open_seq() for _ in seqs]
+        live = list(range(len(seqs)))
+        got = eng.step(slots, [s[:n] for s, n in zip(seqs, lens)], [list(range(n)) for n in lens]).clone()
+        off = 0
+        for i, n in enumerate(lens):
+            assert_logits_close(got[off:off + n], refs[i][:n], dtype, f"{name} batch prompt {i}")
+            off += n
+        step = 0
+        while live:
+            got = eng.step([slots[i] for i in live], [[seqs[i][lens[i] + step]] for i in live]).clone()
+            for r, i in enumerate(live):
+                assert_logits_close(got[r], refs[i][lens[i] + step], dtype, f"{name} seq {i} decode step {step}")
+            step += 1
+            for i in list(live):
+                if step >= dec[i]:
+                    eng.close_seq(slots[i])
+                    live.remove(i)
+            poison_free_pages(eng)
+        eng.cache.check()
+        assert eng.cache.pages.n_held == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding_crosses_pages_and_splits(dtype):
+    """A 3-token prompt, then 300 tokens one by one: crosses page boundaries
+    (64) and the decode kernel's split size (256)."""
+    name = "A"
+    eng = make_engine(name, dtype)
+    poison_all(eng)
+    toks = random_tokens(vocab_of(name), 256 - 3 + 50, 21)[:256]   # max_position_embeddings of A is 256
+    ref = plain_logits(name, toks)
+    s = eng.open_seq()
+    got = [eng.step([s], [toks[:3]], [[0, 1, 2]]).clone()]
+    for t in toks[3:]:
+        got.append(eng.step([s], [[t]]).clone())
+    assert_logits_close(torch.cat(got), ref, dtype, "long decode")
+    with pytest.raises(ValueError, match="context length exceeded"):
+        eng.step([s], [[1]])
+    eng.close_seq(s)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding_over_several_splits(dtype):
+    name = "B"
+    eng = make_engine(name, dtype)
+    toks = random_tokens(vocab_of(name), 512, 22)
+    ref = plain_logits(name, toks)
+    s = eng.open_seq()
+    eng.step([s], [toks[:200]], [[]])
+    got = [eng.step([s], [[t]]).clone() for t in toks[200:]]
+    eng.close_seq(s)
+    assert_logits_close(torch.cat(got), ref[200:], dtype, "decode from 200 to 512")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_first_tokens_of_a_sequence(name, dtype):
+    """Position 0 sees only itself; a one-token prompt, then its first decoded tokens."""
+    eng = make_engine(name, dtype)
+    poison_all(eng)
+    toks = random_tokens(vocab_of(name), 4, 31)
+    ref = plain_logits(name, toks)
+    s = eng.open_seq()
+    got = [eng.step([s], [[t]]).clone() for t in toks]
+    eng.close_seq(s)
+    assert_logits_close(torch.cat(got), ref, dtype, "first tokens")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_padding_and_batch_composition_change_nothing(dtype):
+    """The same request decoded alone, in a batch of 3 (padded to 4 in the
+    captured step) and in a batch of 5 (padded to 8) gives the same logits."""
+    name = "B"
+    eng = make_engine(name, dtype, use_graphs=True)
+    seqs = [random_tokens(vocab_of(name), n, 40 + n) for n in (20, 3, 77, 41, 9)]
+    outs = {}
+    for group in ([0], [0, 1, 2], [0, 1, 2, 3, 4]):
+        slots = [eng.open_seq() for _ in group]
+        eng.step(slots, [seqs[i][:-4] for i in group], [[] for _ in group])
+        rows = []
+        for k in range(4, 0, -1):
+            rows.append(eng.step(slots, [[seqs[i][-k]] for i in group])[0].clone())
+        for s in slots:
+            eng.close_seq(s)
+        outs[len(group)] = torch.stack(rows)
+    assert torch.equal(outs[1], outs[3]) and torch.equal(outs[1], outs[5])
+    assert_logits_close(outs[5], plain_logits(name, seqs[0])[-4:], dtype, "batched decode")
+
+
+def test_step_checks_its_arguments():
+    eng = make_engine("A", "float32")
+    s = eng.open_seq()
+    with pytest.raises(ValueError, match="outside the vocabulary"):
+        eng.step([s], [[512]])
+    with pytest.raises(ValueError, match="outside the vocabulary"):
+        eng.step([s], [[-1]])
+    with pytest.raises(ValueError, match="brings no token"):
+        eng.step([s], [[]])
+    with pytest.raises(ValueError, match="wanted place"):
+        eng.step([s], [[1, 2]], [[2]])
+    with pytest.raises(ValueError, match="twice"):
+        eng.step([s, s], [[1], [2]])
+    from wick_b200.cache import PoolError
+    with pytest.raises(PoolError, match="not open"):
+        eng.step([s + 1], [[1]])
+    assert eng.seq_len(s) == 0, "a refused step changes nothing"
+    out = eng.step([s], [[1, 2, 3]], [[]])
+    assert out.shape == (0, 512) and eng.seq_len(s) == 3
+    eng.close_seq(s)
+
+
+def test_wanted_rows_come_in_order_of_entries_and_want():
+    name, dtype = "A", "float32"
+    eng = make_engine(name, dtype)
+    a, b = random_tokens(512, 9, 50), random_tokens(512, 4, 51)
+    sa, sb = eng.open_seq(), eng.open_seq()
+    got = eng.step([sa, sb], [a, b], [[8, 0], [2]])
+    ra, rb = plain_logits(name, a), plain_logits(name, b)
+    assert_logits_close(got, torch.stack([ra[8], ra[0], rb[2]]), dtype, "want order")
+    eng.close_seq(sa)
+    eng.close_seq(sb)
+
+
+def test_model_with_random_weights_drawn_on_the_device():
+    cfg = wick.config_from_json(CONFIGS["B"])
+    eng = wick.Engine.from_config(cfg, seed=3, dtype="bfloat16", max_tokens=256)
+    s = eng.open_seq()
+    out = eng.step([s], [[1, 2, 3]])
+    assert out.shape == (1, 1000) and torch.isfinite(out).all() and out.abs().max() > 0

@@ -1,0 +1,276 @@
+"""Each kernel alone against a plain PyTorch float32 reference of the same
+operation, at sizes other than the tiny models' (odd widths, vocabularies that
+are no power of two, head sizes 16..128, groups of 1, 2, 5 and 8)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from plain import qwen3_plain as P  # noqa: E402
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def dev(t):
+    return t.to("cuda")
+
+
+def tol(dtype, scale=1.0):
+    return (2e-5 if dtype == torch.float32 else 1.2e-2) * scale
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from wick_b200 import ops
+    return ops
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed(ops, dtype):
+    table = torch.randn(333, 72).to(dtype)
+    tok = torch.tensor([0, 332, 5, 5, 17], dtype=torch.int32)
+    out = ops.embed(dev(table), dev(tok))
+    assert out.dtype == torch.float32 and torch.equal(out.cpu(), table.float()[tok.long()])
+
+
+@pytest.mark.parametrize("out_dtype", DTYPES)
+@pytest.mark.parametrize("width", [72, 1000, 4096 + 8])
+def test_rmsnorm_plain_with_delta_and_with_rows(ops, out_dtype, width):
+    torch.manual_seed(width)
+    x, w = torch.randn(9, width) * 3, 1 + 0.1 * torch.randn(width)
+    ref = P.rms_norm(x, w, 1e-5)
+    got = ops.rmsnorm(dev(x), dev(w), 1e-5, out_dtype)
+    assert got.dtype == out_dtype and (got.float().cpu() - ref).abs().max() < tol(out_dtype, ref.abs().max())
+    # fused residual addition of three partial sums, on selected rows
+    delta = torch.randn(3, 9, width)
+    rows = torch.tensor([7, 2, 2, 0], dtype=torch.int32)
+    xd = dev(x.clone())
+    got = ops.rmsnorm(xd, dev(w), 1e-5, out_dtype, delta=dev(delta), rows=dev(rows))
+    xs = x + ((delta[0] + delta[1]) + delta[2])
+    ref = P.rms_norm(xs[rows.long()], w, 1e-5)
+    assert (got.float().cpu() - ref).abs().max() < tol(out_dtype, ref.abs().max())
+    assert torch.allclose(xd.cpu()[[0, 7]], xs[[0, 7]], atol=1e-6), "the residual is updated in place"
+    assert torch.equal(xd.cpu()[1], x[1]), "rows that were not asked for stay untouched"
+
+
+def test_add_delta(ops):
+    x, d = torch.randn(5, 33), torch.randn(2, 5, 33)
+    got = ops.add_delta(dev(x.clone()), dev(d))
+    assert torch.allclose(got.cpu(), x + (d[0] + d[1]), atol=1e-6)
+
+
+def test_rope_table_uses_float32_angles(ops):
+    inv = P.rope_inv_freq(1e6, 48)
+    pos = torch.tensor([0, 1, 77, 40000], dtype=torch.int32)
+    cos, sin = ops.rope_table(dev(pos), dev(inv))
+    ang = pos.float()[:, None] * inv[None, :]
+    assert (cos.cpu() - torch.cos(ang)).abs().max() < 2e-6 and (sin.cpu() - torch.sin(ang)).abs().max() < 2e-6
+
+
+def _paged(n_pages, n_kv, hd, dtype, fill=float("nan")):
+    return torch.full((n_pages, 2, n_kv, 64, hd), fill, dtype=dtype, device="cuda")
+
+
+class FakeBatch:
+    """The fields of a step batch that the attention kernels read."""
+
+    def __init__(self, q_lens, starts, pages, width=None):
+        from wick_b200.engine.batch import BatchLayout, StepBatch, fill_host, n_q_tiles
+        B = len(q_lens)
+        width = width or max(len(p) for p in pages)
+        lay = BatchLayout(B, sum(q_lens), width, 0, n_q_tiles(q_lens))
+        host = np.zeros(lay.size, dtype=np.int32)
+        fill_host(lay, host, tokens=[[0] * q for q in q_lens], starts=starts, slots=list(range(1, B + 1)),
+                  pages=pages, want=[[] for _ in q_lens])
+        self.sb = StepBatch(lay, torch.from_numpy(host).cuda(), q_lens=q_lens, starts=starts)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads, kv_heads, hd", [(4, 2, 16), (5, 1, 48), (8, 8, 64), (16, 2, 128)])
+def test_qk_norm_rope_append_and_attention(ops, dtype, heads, kv_heads, hd):
+    """Two sequences with a cached prefix each, pages in scrambled order, cache
+    full of NaN where nothing was written: the fused norm/rotation/append kernel,
+    then the prompt kernel and the decode kernel, against the plain parts."""
+    torch.manual_seed(hd + heads)
+    q_lens, starts = [70, 3], [130, 0]
+    totals = [s + q for s, q in zip(starts, q_lens)]
+    pages = [[9, 2, 5, 7], [4]]
+    kv = _paged(12, kv_heads, hd, dtype)
+    qw, kw = 1 + 0.1 * torch.randn(hd), 1 + 0.1 * torch.randn(hd)
+    inv = P.rope_inv_freq(10000.0, hd)
+    eps = 1e-6
+    full = [torch.randn(t, (heads + 2 * kv_heads) * hd).to(dtype) for t in totals]
+
+    def plain_qkv(x):
+        t = x.shape[0]
+        x = x.float()
+        q = x[:, :heads * hd].view(t, heads, hd)
+        k = x[:, heads * hd:(heads + kv_heads) * hd].view(t, kv_heads, hd)
+        v = x[:, (heads + kv_heads) * hd:].view(t, kv_heads, hd)
+        pos = torch.arange(t)
+        return (P.rope(P.rms_norm(q, qw, eps), pos, inv), P.rope(P.rms_norm(k, kw, eps), pos, inv), v)
+
+    # step 1: the prefixes (sequence 0 only), step 2: the new tokens of both
+    fb0 = FakeBatch([starts[0]], [0], [pages[0]], width=4).sb
+    cos, sin = ops.rope_table(fb0.positions, dev(inv))
+    ops.qk_norm_rope_append(dev(full[0][:starts[0]]), heads, kv_heads, hd, q_weight=dev(qw), k_weight=dev(kw),
+                            eps=eps, cos=cos, sin=sin, kv=kv, page_table=fb0.page_table,
+                            seq_of_token=fb0.seq_of_token, positions=fb0.positions)
+    fb = FakeBatch(q_lens, starts, pages).sb
+    new = torch.cat([full[0][starts[0]:], full[1]])
+    cos, sin = ops.rope_table(fb.positions, dev(inv))
+    q = ops.qk_norm_rope_append(dev(new), heads, kv_heads, hd, q_weight=dev(qw), k_weight=dev(kw), eps=eps,
+                                cos=cos, sin=sin, kv=kv, page_table=fb.page_table, seq_of_token=fb.seq_of_token,
+                                positions=fb.positions)
+    refs = [plain_qkv(x) for x in full]
+    ref_q = torch.cat([refs[0][0][starts[0]:], refs[1][0]])
+    assert (q.float().cpu() - ref_q).abs().max() < tol(dtype, 4)
+    # the cache holds k (normed, rotated) and v (raw) at every position, in the right page
+    for b in range(2):
+        for p in (0, totals[b] - 1, min(64, totals[b] - 1)):
+            page = pages[b][p // 64]
+            assert (kv[page, 0, :, p % 64].float().cpu() - refs[b][1][p]).abs().max() < tol(dtype, 4)
+            assert torch.equal(kv[page, 1, :, p % 64].float().cpu(), refs[b][2][p].to(dtype).float())
+    # prompt attention over prefix + new tokens
+    out = ops.attention_prompt(q, kv, fb, 1 / math.sqrt(hd))
+    ref_o = []
+    for b in range(2):
+        qq, kk, vv = refs[b]
+        if dtype == torch.bfloat16:           # the kernel reads the rounded cache
+            qq, kk, vv = (t.to(dtype).float() for t in (qq, kk, vv))
+        ref_o.append(P.causal_attention(qq, kk, vv)[starts[b]:])
+    ref_o = torch.cat(ref_o)
+    assert torch.isfinite(out.float()).all(), "a NaN from an unwritten cache position leaked"
+    assert (out.float().cpu() - ref_o).abs().max() < tol(dtype, 2)
+    # decode attention: the last token of each sequence alone
+    fd = FakeBatch([1, 1], [t - 1 for t in totals], pages).sb
+    last = torch.tensor([q_lens[0] - 1, sum(q_lens) - 1], device="cuda")
+    scratch = torch.empty(ops.attention_decode_scratch_floats(2, heads, hd, fd.max_kv_len), device="cuda")
+    outd = ops.attention_decode(q[last].contiguous(), kv, fd, 1 / math.sqrt(hd), scratch)
+    assert torch.isfinite(outd.float()).all()
+    assert (outd.float().cpu() - ref_o[last.cpu()]).abs().max() < tol(dtype, 2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_one_far_key_among_hundreds(ops, dtype):
+    """One key far back gets a score that dominates: the output must be its
+    value.  Random keys would hide a kernel that skips a page or a split."""
+    heads, kv_heads, hd = 4, 2, 32
+    n = 700
+    for far in (3, 64 * 4 + 1, 511, 640):
+        torch.manual_seed(far)
+        k = torch.randn(n, kv_heads, hd) * 0.1
+        v = torch.randn(n, kv_heads, hd)
+        q = torch.randn(1, heads, hd) * 0.1
+        k[far] = 0
+        k[far, :, 0] = 8.0
+        q[0, :, 0] = 40.0                                   # score 40*8/sqrt(32) = 56 above all others
+        kv = _paged(13, kv_heads, hd, dtype)
+        pages = [list(range(12, 12 - 11, -1))]              # 11 pages in descending order
+        for p in range(n):
+            kv[pages[0][p // 64], 0, :, p % 64] = k[p].to(dtype).cuda()
+            kv[pages[0][p // 64], 1, :, p % 64] = v[p].to(dtype).cuda()
+        fd = FakeBatch([1], [n - 1], pages).sb
+        scratch = torch.empty(ops.attention_decode_scratch_floats(1, heads, hd, n), device="cuda")
+        out = ops.attention_decode(dev(q.to(dtype)), kv, fd, 1 / math.sqrt(hd), scratch).float().cpu()
+        want = v[far].to(dtype).float().repeat_interleave(heads // kv_heads, 0)
+        assert (out[0] - want).abs().max() < 1e-2, f"decode kernel missed key {far}"
+        # the same through the prompt kernel: 5 new tokens whose last one carries the query
+        qs = torch.zeros(5, heads, hd)
+        qs[4] = q[0]
+        fp = FakeBatch([5], [n - 5], pages).sb
+        outp = ops.attention_prompt(dev(qs.to(dtype)), kv, fp, 1 / math.sqrt(hd)).float().cpu()
+        assert (outp[4] - want).abs().max() < 1e-2, f"prompt kernel missed key {far}"
+
+
+@pytest.mark.parametrize("m, n, k", [(1, 72, 64), (7, 333, 100), (130, 192, 96), (64, 1000, 72)])
+@pytest.mark.parametrize("combo", ["f32", "bf16", "bf16_f32", "f32_gated", "bf16_gated"])
+def test_gemm_simt(ops, m, n, k, combo):
+    torch.manual_seed(m * n + k)
+    dt = torch.float32 if combo.startswith("f32") else torch.bfloat16
+    out_dt = torch.float32 if combo in ("f32", "bf16_f32", "f32_gated") else torch.bfloat16
+    gated = combo.endswith("gated")
+    x = torch.randn(m, k).to(dt)
+    w = (torch.randn(2 * n if gated else n, k) / math.sqrt(k)).to(dt)
+    got = ops.gemm_simt(dev(x), dev(w), out_dt, gated=gated).float().cpu()
+    y = x.double() @ w.double().T
+    ref = (y[:, :n] / (1 + torch.exp(-y[:, :n])) * y[:, n:]) if gated else y
+    assert got.shape == (m, n)
+    assert (got - ref.float()).abs().max() < (2e-5 if out_dt == torch.float32 else 2e-2)
+
+
+def test_gemm_rows_do_not_depend_on_the_batch(ops):
+    x = torch.randn(65, 96)
+    w = torch.randn(160, 96)
+    full = ops.gemm_simt(dev(x), dev(w), torch.float32)
+    one = ops.gemm_simt(dev(x[13:14].contiguous()), dev(w), torch.float32)
+    assert torch.equal(full[13:14], one)
+
+
+def test_argmax_first_maximum(ops):
+    x = torch.randn(6, 151936 // 8 + 3)
+    x[1, 77] = x[1, 5000] = 50.0                    # a tie: the first index wins
+    x[2, 0] = float("nan")                          # nothing compares greater than a leading NaN
+    x[3, 10] = float("nan")
+    x[4] = float("-inf")
+    got = ops.argmax(dev(x)).tolist()
+    assert got == [P.argmax_first(r) for r in x]
+    assert got[1] == 77 and got[2] == 0 and got[4] == 0
+
+
+def test_sample_temperature_follows_the_cumulative_distribution(ops):
+    torch.manual_seed(0)
+    vocab = 5003
+    logits = torch.randn(64, vocab) * 2
+    u = torch.rand(64)
+    u[0], u[1] = 0.0, 0.9999999
+    for temp in (0.7, 1.5):
+        got = ops.sample_temperature(dev(logits), temp, dev(u)).tolist()
+        p = torch.softmax(logits.double() / temp, -1)
+        c = p.cumsum(-1)
+        for i, t in enumerate(got):
+            lo = c[i, t - 1].item() if t > 0 else 0.0
+            assert lo - 1e-5 <= u[i].item() <= c[i, t].item() + 1e-5, (i, t)
+    # empirical frequencies (sampler.rs:164-172): 1/4 and 3/4
+    l2 = torch.tensor([[0.0, math.log(3.0)]]).repeat(4000, 1)
+    got = ops.sample_temperature(dev(l2), 1.0, dev(torch.rand(4000)))
+    assert abs(got.float().mean().item() - 0.75) < 0.03
+
+
+@pytest.mark.parametrize("vocab, k", [(333, 1), (1000, 40), (5003, 333), (151936, 40), (2048, 1024)])
+def test_top_k_sorted_with_index_tie_break(ops, vocab, k):
+    torch.manual_seed(vocab + k)
+    x = torch.randn(5, vocab)
+    x[1, :] = x[1, :].round()                       # many ties
+    x[2, 7] = x[2, 900 % vocab] = 99.0
+    x[3, :] = 1.0                                   # all equal: the lowest indices
+    vals, idx = ops.top_k(dev(x), k)
+    vals, idx = vals.cpu(), idx.cpu()
+    for r in range(5):
+        order = sorted(range(vocab), key=lambda i: (-x[r, i].item(), i))[:k]
+        assert idx[r].tolist() == order
+        assert torch.equal(vals[r], x[r][order])
+
+
+def test_repetition_penalty(ops):
+    x = torch.tensor([[2.0, -2.0, 4.0, 1.0], [1.0, 1.0, -1.0, 0.0]])
+    got = ops.repetition_penalty(dev(x.clone()), [[0, 1, 1, 0], [2, 9]], 2.0).cpu()
+    assert torch.equal(got, torch.tensor([[1.0, -4.0, 4.0, 1.0], [1.0, 1.0, -2.0, 0.0]]))
+
+
+def test_kernels_refuse_what_they_cannot_do(ops):
+    from wick_b200.ops import KernelError
+    with pytest.raises(KernelError, match="CUDA tensor"):
+        ops.embed(torch.zeros(3, 4), torch.zeros(2, dtype=torch.int32))
+    with pytest.raises(KernelError, match="float16"):
+        ops.embed(torch.zeros(3, 4, dtype=torch.float16, device="cuda"), torch.zeros(2, dtype=torch.int32, device="cuda"))
+    with pytest.raises(KernelError, match="multiple of 16"):
+        ops.attention_prompt(torch.zeros(1, 2, 24, device="cuda"), torch.zeros(1, 2, 1, 64, 24, device="cuda"),
+                             FakeBatch([1], [0], [[0]]).sb, 1.0)
+    with pytest.raises(KernelError, match="top_k"):
+        ops.top_k(torch.zeros(1, 5000, device="cuda"), 2000)
+    with pytest.raises(KernelError, match="contiguous"):
+        ops.argmax(torch.zeros(4, 8, device="cuda").t())

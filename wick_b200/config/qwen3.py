@@ -142,7 +142,7 @@ class Qwen3Config(ModelConfig):
 
     def to_json(self) -> Dict[str, Any]:
         j: Dict[str, Any] = {
-            "architectures": ["Qwen3ForCausalLM"],
+            "architectures": ["Qwen3ForCausalLM" if self.architecture == "qwen3" else self.architecture],
             "model_type": "qwen3",
             "hidden_size": self.hidden_size,
             "intermediate_size": self.intermediate_size,
