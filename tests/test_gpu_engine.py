@@ -161,7 +161,7 @@ def test_padding_and_batch_composition_change_nothing(dtype):
     captured step) and in a batch of 5 (padded to 8) gives the same logits."""
     name = "B"
     eng = make_engine(name, dtype, use_graphs=True)
-    seqs = [random_tokens(vocab_of(name), n, 40 + n) for n in (20, 3, 77, 41, 9)]
+    seqs = [random_tokens(vocab_of(name), n, 40 + n) for n in (20, 6, 77, 41, 9)]
     outs = {}
     for group in ([0], [0, 1, 2], [0, 1, 2, 3, 4]):
         slots = [eng.open_seq() for _ in group]

@@ -250,7 +250,10 @@ def test_top_k_sorted_with_index_tie_break(ops, vocab, k):
     vals, idx = ops.top_k(dev(x), k)
     vals, idx = vals.cpu(), idx.cpu()
     for r in range(5):
-        order = sorted(range(vocab), key=lambda i: (-x[r, i].item(), i))[:k]
+        # descending in the total order of floats (-0.0 below +0.0, as f32::total_cmp), ties by index
+        bits = x[r].numpy().view(np.uint32).astype(np.int64)
+        keys = np.where(bits & 0x80000000, ~bits & 0xFFFFFFFF, bits | 0x80000000)
+        order = sorted(range(vocab), key=lambda i: (-int(keys[i]), i))[:k]
         assert idx[r].tolist() == order
         assert torch.equal(vals[r], x[r][order])
 

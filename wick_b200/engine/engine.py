@@ -236,9 +236,13 @@ class Engine:
         f_slots = list(slots) + [0] * pad
         f_pages = [cache.pages_of(s)[:(st + 1 + PAGE - 1) // PAGE] for s, st in zip(slots, starts)] + [[0]] * pad
         f_want = [[0]] * n_pad            # the graph always computes every row's logits
-        self._upload(g.layout, g.buffer, tokens=f_tokens, starts=f_starts, slots=f_slots, pages=f_pages, want=f_want)
         if g.graph is None:
+            # Capture (and its warm-up run) on a batch of padding entries only, so
+            # that no live sequence's cache or state is touched twice.
+            self._upload(g.layout, g.buffer, tokens=[[0]] * n_pad, starts=[0] * n_pad, slots=[0] * n_pad,
+                         pages=[[0]] * n_pad, want=f_want)
             self._capture(g)
+        self._upload(g.layout, g.buffer, tokens=f_tokens, starts=f_starts, slots=f_slots, pages=f_pages, want=f_want)
         g.graph.replay()
         rows = [b for b in range(B) for _ in want[b]]
         if rows == list(range(B)):
