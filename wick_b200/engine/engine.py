@@ -21,6 +21,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
+from .. import ops
 from ..cache import PAGE, Cache
 from ..config.base import ModelConfig, get_architecture, load_config
 from ..models.model import Model
@@ -244,6 +245,7 @@ class Engine:
             self._capture(g)
         self._upload(g.layout, g.buffer, tokens=f_tokens, starts=f_starts, slots=f_slots, pages=f_pages, want=f_want)
         g.graph.replay()
+        ops.launches[0] += g.kernels
         rows = [b for b in range(B) for _ in want[b]]
         if rows == list(range(B)):
             return g.logits[:B]
@@ -270,11 +272,14 @@ class Engine:
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         self.workspace.frozen = True
+        before = ops.launches[0]
         try:
             with torch.cuda.graph(graph):
                 g.logits = run()
         finally:
             self.workspace.frozen = False
+        g.kernels = ops.launches[0] - before
+        ops.launches[0] = before
         # The graph holds raw pointers into the scratch buffers: keep those alive
         # even if the workspace later replaces them by larger ones.
         g.keepalive = dict(self.workspace.buffers)

@@ -57,13 +57,18 @@ class _Lib:
             self._fns[name] = f
         return f
 
-    def call(self, name: str, sig: str, *args):
+    def call(self, name: str, sig: str, *args, kernels: int = 1):
         rc = self.fn(name, sig)(*args)
         if rc != 0:
             raise KernelError(self._lib.wick_last_error().decode("utf-8", "replace"))
+        launches[0] += kernels
 
 
 _libs: Dict[str, _Lib] = {}
+
+# Kernels launched through this module so far (a captured step counts them once,
+# at capture; the engine adds them again at every replay).
+launches = [0]
 
 
 def _core() -> _Lib:
@@ -287,7 +292,7 @@ def attention_decode(q: torch.Tensor, kv: torch.Tensor, batch, scale: float, scr
     mk = batch.max_kv_len if max_kv_len is None else max_kv_len
     _attn(hd).call(f"wick_attn_decode_{_dt(q)}", "pppplpiipiiifp", _p(q), _p(kv), _p(out),
                    _p(scratch), scratch.numel(), _p(batch.kv_len), n, mk, _p(batch.page_table), batch.table_width,
-                   n_heads, n_kv, float(scale), _stream())
+                   n_heads, n_kv, float(scale), _stream(), kernels=2)
     return out
 
 
