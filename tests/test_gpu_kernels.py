@@ -277,3 +277,63 @@ def test_kernels_refuse_what_they_cannot_do(ops):
         ops.top_k(torch.zeros(1, 5000, device="cuda"), 2000)
     with pytest.raises(KernelError, match="contiguous"):
         ops.argmax(torch.zeros(4, 8, device="cuda").t())
+
+
+# ---- the tensor-core matrix product ------------------------------------------
+def _tc_ref(x, w, gated):
+    y = x.double() @ w.double().T
+    if gated:
+        n = w.shape[0] // 2
+        y = y[:, :n] / (1 + torch.exp(-y[:, :n])) * y[:, n:]
+    return y.float()
+
+
+@pytest.mark.parametrize("t, n, k, gated", [
+    (1, 128, 64, False), (5, 333, 72, False), (8, 256, 128, False), (64, 1000, 96, False), (3, 200, 104, True),
+    (16, 384, 1024, False), (65, 333, 72, False), (128, 16, 64, False), (300, 520, 200, False), (300, 520, 200, True),
+    (1000, 1024, 512, True), (33, 4096, 4096, False)])
+def test_gemm_tensor_core_both_ways_round(t, n, k, gated):
+    """Few tokens (weights as the 128-row operand, transposed output, split inner
+    dimension) and many tokens (tokens as the 128-row operand), plain and gated,
+    with ragged edges in every dimension, against a float64 product."""
+    from wick_b200.ops import gemm_tc as G
+    torch.manual_seed(t + n + k)
+    x = torch.randn(t, k).bfloat16()
+    w = (torch.randn(2 * n if gated else n, k) / math.sqrt(k)).bfloat16()
+    plan = G.plan_for(dev(w), gated)
+    assert plan is not None
+    ref = _tc_ref(x, w, gated)
+    got32 = plan.forward(dev(x), torch.float32)
+    got16 = plan.forward(dev(x), torch.bfloat16)
+    assert got32.shape == (t, n)
+    assert (got32.cpu() - ref).abs().max() < 2e-4 * max(1.0, ref.abs().max())
+    assert (got16.float().cpu() - ref).abs().max() < 1e-2 * max(1.0, ref.abs().max())
+    if not gated:
+        parts = plan.forward_delta(dev(x))
+        assert parts.dtype == torch.float32 and parts.shape[1:] == (t, n)
+        assert (parts.sum(0).cpu() - ref).abs().max() < 2e-4 * max(1.0, ref.abs().max())
+        if t <= G.SMALL and k >= 1024:
+            assert parts.shape[0] > 1, "a matrix with few row slabs splits its inner dimension"
+    G.check_status()
+    # the CUDA-core kernel is the plain twin of this one
+    twin = ops_gemm_simt(dev(x), dev(w), gated)
+    assert (got32 - twin).abs().max() < (1e-2 if gated else 2e-4) * max(1.0, ref.abs().max())   # gated twin: bf16 out
+
+
+def ops_gemm_simt(x, w, gated):
+    from wick_b200 import ops
+    return ops.gemm_simt(x, w, torch.bfloat16 if gated else torch.float32, gated=gated).float()
+
+
+def test_gemm_tensor_core_rows_do_not_depend_on_the_batch():
+    from wick_b200.ops import gemm_tc as G
+    torch.manual_seed(5)
+    w = dev((torch.randn(512, 2048) / 45).bfloat16())
+    x = dev(torch.randn(40, 2048).bfloat16())
+    plan = G.plan_for(w)
+    full = plan.forward_delta(x)
+    for rows in (1, 7, 16, 17):
+        part = plan.forward_delta(x[:rows].contiguous())
+        assert torch.equal(part, full[:, :rows]), rows
+    assert G.plan_for(dev(torch.zeros(64, 100, dtype=torch.bfloat16))) is None, "rows of 200 bytes cannot be fetched by TMA"
+    assert G.plan_for(dev(torch.zeros(64, 96))) is None, "float32 weights take the CUDA-core kernel"

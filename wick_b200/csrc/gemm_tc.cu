@@ -1,0 +1,381 @@
+// D[m, n] = sum_k A[m, k] * B[n, k] for bfloat16 operands that are both
+// contiguous along k, on the 5th-generation tensor cores of sm_100a:
+//
+//   * TMA (cp.async.bulk.tensor, 128-byte swizzle) stages 128 x 64 tiles of A and
+//     bn x 64 tiles of B in a ring of shared-memory buffers;
+//   * one elected thread issues tcgen05.mma (M = 128, N = bn, K = 16 per
+//     instruction) with the float32 accumulator in tensor memory;
+//   * four warps read the accumulator back with tcgen05.ld and write the result.
+//
+// The same kernel serves both shapes of work.  Prompts: A = activations
+// [tokens, k], B = weights [out, k], D written row-major [tokens, out].  Decode
+// (few tokens): A = weights, B = activations (bn = tokens rounded up to 16), D
+// written transposed, so that the 128-row side of the instruction is always
+// full and every CTA streams a 128-row slab of the weight matrix.  Options:
+// a gated pair (two accumulators, silu(g) * u in the epilogue; wick
+// src/model.rs:493-501), float32 or bfloat16 output, and a split of the k range
+// over blockIdx.z into float32 partial sums that the consumer adds in index
+// order.  Each output element is accumulated along k in index order within a
+// split, whatever the tile it falls into, so a row's result does not depend on
+// the other rows of the batch.
+//
+// Every wait on an mbarrier is bounded (about one second); when a wait gives up,
+// the kernel records a code in *status, stops waiting anywhere, lets copies in
+// flight land, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace wick {
+
+constexpr int BM = 128;            // rows of the A tile = M of the instruction
+constexpr int BK = 64;             // k per stage: 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int MAX_STAGES = 12;
+constexpr int NUM_THREADS = 192;   // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-5: epilogue
+
+struct GemmParams {
+    int a_rows;                    // valid rows of A (outputs beyond are not written)
+    int b_rows;                    // valid rows of B
+    int bn;                        // rows of a B tile = N of the instruction (multiple of 16, <= 256)
+    int k_blocks;                  // ceil(k / 64)
+    int k_blocks_per_split;
+    int stages;
+    int gated;                     // 0 none, 1 the pair lives in A, 2 the pair lives in B
+    int pair_offset;               // row offset of the second half of the pair
+    int transposed;                // 0: out[m * ldo + n], 1: out[n * ldo + m]
+    int out_f32;
+    long long ldo;
+    long long split_stride;        // elements between the partial results of two splits
+    void* out;
+    int* status;
+};
+
+// ---- PTX wrappers ------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ uint64_t global_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait.  Returns false (and raises the block's abort flag) after ~1 s.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+    if (*abort_flag) return false;
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_ns();
+    for (uint32_t spin = 0;; ++spin) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((spin & 255u) == 255u) {
+            if (*abort_flag) return false;
+            if (global_ns() - t0 > 1000000000ull) {
+                *abort_flag = 1;
+                if (status) atomicCAS(status, 0, code);
+                return false;
+            }
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint64_t* bar, void* dst, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, float* v) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a tile whose rows are 128 bytes (64 bf16)
+// apart with the 128-byte swizzle, eight-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);            // start address, 16-byte units
+    d |= (uint64_t)1 << 16;                             // leading byte offset (unused with a swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;                   // stride byte offset: 8 rows * 128 bytes
+    d |= (uint64_t)1 << 46;                             // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                             // 128-byte swizzle
+    return d;
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t full_bar[MAX_STAGES];
+    __shared__ uint64_t empty_bar[MAX_STAGES];
+    __shared__ uint64_t acc_bar;
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * BM;
+    const int n0 = blockIdx.y * p.bn;
+    const int kb_begin = blockIdx.z * p.k_blocks_per_split;
+    const int kb_end = min(p.k_blocks, kb_begin + p.k_blocks_per_split);
+    const int n_kb = kb_end - kb_begin;
+
+    const int a_tiles = p.gated == 1 ? 2 : 1, b_tiles = p.gated == 2 ? 2 : 1;
+    const uint32_t a_bytes = BM * BK * 2, b_bytes = (uint32_t)p.bn * BK * 2;
+    const uint32_t stage_bytes = a_tiles * a_bytes + b_tiles * b_bytes;
+    uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const int n_acc = p.gated ? 2 : 1;
+    uint32_t tmem_cols = 32;
+    while (tmem_cols < (uint32_t)(n_acc * p.bn)) tmem_cols <<= 1;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(&acc_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(tmem_cols));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            for (int i = 0; i < n_kb; ++i) {
+                const int s = i % p.stages;
+                const uint32_t round = i / p.stages;
+                if (!mbar_wait(&empty_bar[s], (round & 1) ^ 1, &abort_flag, p.status, 1)) break;
+                uint8_t* st = tiles + (size_t)s * stage_bytes;
+                mbar_expect_tx(&full_bar[s], stage_bytes);
+                const int kx = (kb_begin + i) * BK;
+                tma_load_2d(&map_a, &full_bar[s], st, kx, m0);
+                if (a_tiles == 2) tma_load_2d(&map_a, &full_bar[s], st + a_bytes, kx, m0 + p.pair_offset);
+                uint8_t* sb = st + a_tiles * a_bytes;
+                tma_load_2d(&map_b, &full_bar[s], sb, kx, n0);
+                if (b_tiles == 2) tma_load_2d(&map_b, &full_bar[s], sb + b_bytes, kx, n0 + p.pair_offset);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            // kind::f16, A and B bfloat16 and k-major, float32 accumulator, M = 128, N = bn
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            bool ok = true;
+            for (int i = 0; i < n_kb && ok; ++i) {
+                const int s = i % p.stages;
+                const uint32_t round = i / p.stages;
+                ok = mbar_wait(&full_bar[s], round & 1, &abort_flag, p.status, 2);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t sa = smem_u32(tiles + (size_t)s * stage_bytes);
+                const uint32_t sb = sa + a_tiles * a_bytes;
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+                    const uint64_t da = smem_desc(sa + k * UMMA_K * 2), db = smem_desc(sb + k * UMMA_K * 2);
+                    tc_mma(tmem_base, da, db, idesc, acc);
+                    if (p.gated == 1) tc_mma(tmem_base + p.bn, smem_desc(sa + a_bytes + k * UMMA_K * 2), db, idesc, acc);
+                    if (p.gated == 2) tc_mma(tmem_base + p.bn, da, smem_desc(sb + b_bytes + k * UMMA_K * 2), idesc, acc);
+                }
+                tc_commit(&empty_bar[s]);          // the stage is free once these instructions have read it
+            }
+            tc_commit(&acc_bar);                   // the accumulator is complete
+        }
+    } else {
+        // ---------------- epilogue: tensor memory -> global ----------------
+        const int q = warp & 3;                    // this warp reads lanes 32q .. 32q+31
+        const bool ok = mbar_wait(&acc_bar, 0, &abort_flag, p.status, 3);
+        tc_fence_after();
+        const int m = m0 + q * 32 + lane;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+        char* out_base = (char*)p.out + (size_t)blockIdx.z * p.split_stride * (p.out_f32 ? 4 : 2);
+        if (ok && n_kb > 0) {
+            for (int c0 = 0; c0 < p.bn; c0 += 16) {
+                float v[16];
+                tc_ld16(lane_addr + c0, v);
+                if (p.gated) {
+                    float u[16];
+                    tc_ld16(lane_addr + p.bn + c0, u);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] = v[j] / (1.0f + expf(-v[j])) * u[j];
+                }
+                if (m < p.a_rows) {
+                    if (!p.transposed) {
+                        const int n_left = p.b_rows - (n0 + c0);
+                        const long long off = (long long)m * p.ldo + n0 + c0;
+                        if (p.out_f32) {
+                            float* o = (float*)out_base + off;
+                            if (n_left >= 16 && (off & 3) == 0) {
+#pragma unroll
+                                for (int j = 0; j < 16; j += 4) *(float4*)(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                            } else {
+                                for (int j = 0; j < 16 && j < n_left; ++j) o[j] = v[j];
+                            }
+                        } else {
+                            __nv_bfloat16* o = (__nv_bfloat16*)out_base + off;
+                            if (n_left >= 16 && (off & 7) == 0) {
+                                uint4 w[2];
+                                __nv_bfloat162* h = (__nv_bfloat162*)w;
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                                *(uint4*)o = w[0];
+                                *(uint4*)(o + 8) = w[1];
+                            } else {
+                                for (int j = 0; j < 16 && j < n_left; ++j) o[j] = __float2bfloat16_rn(v[j]);
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const int n = n0 + c0 + j;
+                            if (n < p.b_rows) {
+                                const long long off = (long long)n * p.ldo + m;
+                                if (p.out_f32) ((float*)out_base)[off] = v[j];
+                                else ((__nv_bfloat16*)out_base)[off] = __float2bfloat16_rn(v[j]);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (abort_flag) {
+        // Copies that were already issued may still be in flight: give them time
+        // to land before this block's shared memory is given up.
+        const uint64_t t0 = global_ns();
+        while (global_ns() - t0 < 2000000ull) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols));
+    }
+}
+
+// ---- host side ---------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// A [rows, k] bfloat16 matrix, row-major, as a TMA descriptor with boxes of box_rows x 64.
+static int make_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t k, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    WICK_REQUIRE(fn != nullptr, "gemm_tc: the driver does not provide cuTensorMapEncodeTiled");
+    WICK_REQUIRE(((uintptr_t)ptr & 15) == 0, "gemm_tc: operand is not 16-byte aligned");
+    WICK_REQUIRE(k % 8 == 0, "gemm_tc: inner size %lld is not a multiple of 8 (16-byte rows)", (long long)k);
+    cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    WICK_REQUIRE(r == CUDA_SUCCESS, "gemm_tc: cuTensorMapEncodeTiled failed with code %d (rows %lld, k %lld, box %d)",
+                 (int)r, (long long)rows, (long long)k, box_rows);
+    return 0;
+}
+
+}  // namespace wick
+
+using namespace wick;
+
+// a: [a_total_rows, k] bf16 (the 128-row side), b: [b_total_rows, k] bf16.
+// a_rows / b_rows: rows that produce output (for a gated pair: rows of ONE half;
+// the other half starts pair_offset rows further).
+// gated: 0 none, 1 pair in a, 2 pair in b.  transposed: out[n * ldo + m].
+// splits > 1 needs out_f32; partial s lies split_stride elements after s - 1.
+// status: device int that receives a non-zero code if a wait inside the kernel gave up.
+WICK_API int wick_gemm_tc(const void* a, long long a_total_rows, int a_rows, const void* b, long long b_total_rows,
+                          int b_rows, int k, int bn, int gated, int pair_offset, int transposed, int out_f32,
+                          void* out, long long ldo, int splits, long long split_stride, int max_smem_bytes, int* status,
+                          void* stream) {
+    WICK_REQUIRE(bn % 16 == 0 && bn >= 16 && bn <= 256, "gemm_tc: tile width %d must be a multiple of 16 in [16, 256]", bn);
+    WICK_REQUIRE(!(gated == 2 && bn > 128) , "gemm_tc: a gated pair needs two accumulators: tile width <= 128");
+    WICK_REQUIRE(gated >= 0 && gated <= 2 && splits >= 1, "gemm_tc: bad options");
+    WICK_REQUIRE(splits == 1 || (out_f32 && !gated), "gemm_tc: a split inner dimension needs plain float32 partial sums");
+    WICK_REQUIRE(a_rows > 0 && b_rows >= 0 && k > 0, "gemm_tc: bad sizes");
+    if (b_rows == 0) return 0;
+    const int k_blocks = ceil_div(k, BK);
+    WICK_REQUIRE(splits <= k_blocks, "gemm_tc: %d splits over %d blocks of the inner dimension", splits, k_blocks);
+    const int per_split = ceil_div(k_blocks, splits);
+    WICK_REQUIRE((long long)(splits - 1) * per_split < k_blocks, "gemm_tc: a split would be empty");
+    CUtensorMap map_a, map_b;
+    if (int e = make_map(&map_a, a, a_total_rows, k, BM)) return e;
+    if (int e = make_map(&map_b, b, b_total_rows, k, bn)) return e;
+    const int stage_bytes = (gated == 1 ? 2 : 1) * BM * BK * 2 + (gated == 2 ? 2 : 1) * bn * BK * 2;
+    int budget = max_smem_bytes > 0 ? max_smem_bytes : 200 * 1024;
+    if (budget > 220 * 1024) budget = 220 * 1024;
+    int stages = (budget - 1024) / stage_bytes;
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    if (stages > per_split) stages = per_split < 2 ? 2 : per_split;
+    WICK_REQUIRE(stages >= 2, "gemm_tc: %d bytes of shared memory hold fewer than two stages of %d bytes", budget, stage_bytes);
+    const int smem = stages * stage_bytes + 1024;
+    static int raised = 0;
+    if (smem > raised) {
+        WICK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 221 * 1024));
+        raised = 221 * 1024;
+    }
+    GemmParams p;
+    p.a_rows = a_rows; p.b_rows = b_rows; p.bn = bn; p.k_blocks = k_blocks; p.k_blocks_per_split = per_split;
+    p.stages = stages; p.gated = gated; p.pair_offset = pair_offset; p.transposed = transposed; p.out_f32 = out_f32;
+    p.ldo = ldo; p.split_stride = split_stride; p.out = out; p.status = status;
+    dim3 grid(ceil_div(a_rows, BM), ceil_div(b_rows, bn), splits);
+    WICK_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "gemm_tc: grid limit");
+    gemm_tc_kernel<<<grid, NUM_THREADS, smem, (cudaStream_t)stream>>>(map_a, map_b, p);
+    return check_launch("gemm_tc");
+}

@@ -110,7 +110,7 @@ class Engine:
             use_graphs = os.environ.get("WICK_B200_NO_GRAPHS", "") == ""
         self.use_graphs = use_graphs
         self._graphs: Dict[Tuple[int, int], _DecodeGraph] = {}
-        self.kernel_launches = 0
+        self._steps_since_check = 0
 
     # ---- construction ----------------------------------------------------
     @classmethod
@@ -133,6 +133,14 @@ class Engine:
         eng = cls(model, max_tokens=max_tokens, **kw)
         eng.config = cfg
         return eng
+
+    def check_kernels(self) -> None:
+        """Raise if a kernel reported that it gave up a bounded wait (this
+        synchronises the device, so it runs only now and then)."""
+        self._steps_since_check = 0
+        if self.dtype == torch.bfloat16:
+            from ..ops import gemm_tc
+            gemm_tc.check_status()
 
     # ---- sequences ---------------------------------------------------------
     def open_seq(self) -> int:
@@ -207,7 +215,11 @@ class Engine:
         batch = StepBatch(layout, dev, q_lens=q_lens, starts=starts)
         batch.workspace = self.workspace
         batch.kv_bound = batch.max_kv_len
-        return self.model.forward(batch, cache)
+        logits = self.model.forward(batch, cache)
+        self._steps_since_check += 1
+        if self._steps_since_check >= 64:
+            self.check_kernels()
+        return logits
 
     # ---- captured decode -------------------------------------------------------
     @staticmethod
@@ -284,3 +296,4 @@ class Engine:
         # even if the workspace later replaces them by larger ones.
         g.keepalive = dict(self.workspace.buffers)
         g.graph = graph
+        self.check_kernels()

@@ -1,12 +1,130 @@
-"""Tensor-core (tcgen05) matrix products for bfloat16 weights."""
+"""Plans for the tensor-core (tcgen05) matrix product of ``csrc/gemm_tc.cu``.
+
+A plan belongs to one bfloat16 weight matrix [out, in] and decides, per call,
+which way round the kernel runs:
+
+* few tokens (at most 64): the weights are the 128-row operand, the tokens the
+  narrow one (tile width = tokens rounded up to 16), the result is written
+  transposed.  Matrices with few 128-row slabs split their inner dimension over
+  several blocks, so that enough of them stream weights at once; the float32
+  partial sums are added by the consumer in index order.  The number of splits
+  depends on the matrix alone, never on the batch.
+* more tokens: the tokens are the 128-row operand, weight tiles are 256 rows
+  (128 + 128 for a gated pair) wide.
+
+Inner sizes that are no multiple of 8 (rows that are no multiple of 16 bytes
+cannot be fetched by TMA) have no plan; the caller then uses the CUDA-core kernel.
+"""
 from __future__ import annotations
 
 from typing import Optional
 
 import torch
 
+from . import KernelError, _Lib, _libs, _p, _stream, launches  # noqa: F401
 
-def plan_for(weight: torch.Tensor, gated: bool = False):
-    """A plan object with ``forward`` / ``forward_delta`` for this weight, or
-    None where the tensor-core kernels do not take its sizes."""
-    return None
+SMALL = 64                  # up to this many tokens the weights are the 128-row operand
+N_SMS = 148
+
+_status: Optional[torch.Tensor] = None
+
+
+def _lib() -> _Lib:
+    lib = _libs.get("gemm_tc")
+    if lib is None:
+        lib = _libs["gemm_tc"] = _Lib("wick_gemm_tc", ["gemm_tc.cu"])
+    return lib
+
+
+def status_tensor(device) -> torch.Tensor:
+    global _status
+    if _status is None or _status.device != device:
+        _status = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status
+
+
+def check_status() -> None:
+    """Raise if a tensor-core kernel gave up waiting (synchronises the device)."""
+    if _status is not None:
+        code = int(_status.item())
+        if code != 0:
+            _status.zero_()
+            what = {1: "a free shared-memory stage", 2: "a TMA copy", 3: "the accumulator"}.get(code, "?")
+            raise KernelError(f"gemm_tc: a kernel gave up waiting for {what} (code {code}); its output is invalid")
+
+
+_SIG = "plipliiiiiiiplilipp"
+
+
+def gemm_tc(a: torch.Tensor, a_rows: int, b: torch.Tensor, b_rows: int, *, bn: int, out: torch.Tensor, ldo: int,
+            gated: int = 0, pair_offset: int = 0, transposed: bool = False, splits: int = 1, split_stride: int = 0,
+            max_smem: int = 0) -> None:
+    """The raw kernel call (see ``wick_gemm_tc`` in gemm_tc.cu)."""
+    for nm, t in (("a", a), ("b", b)):
+        if not (t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous() and t.dim() == 2):
+            raise KernelError(f"gemm_tc: {nm} must be a contiguous 2-D bfloat16 CUDA tensor")
+    if a.shape[1] != b.shape[1]:
+        raise KernelError(f"gemm_tc: inner sizes differ: {a.shape[1]} and {b.shape[1]}")
+    if out.dtype not in (torch.float32, torch.bfloat16) or not out.is_contiguous():
+        raise KernelError("gemm_tc: out must be contiguous float32 or bfloat16")
+    st = status_tensor(a.device)
+    _lib().call("wick_gemm_tc", _SIG, _p(a), a.shape[0], a_rows, _p(b), b.shape[0], b_rows, a.shape[1], bn, gated,
+                pair_offset, 1 if transposed else 0, 1 if out.dtype == torch.float32 else 0, _p(out), ldo, splits,
+                split_stride, max_smem, _p(st), _stream())
+
+
+def _ceil16(n: int) -> int:
+    return (n + 15) // 16 * 16
+
+
+class Plan:
+    def __init__(self, weight: torch.Tensor, gated: bool):
+        self.w = weight
+        self.gated = gated
+        self.rows, self.k = weight.shape
+        self.n_out = self.rows // 2 if gated else self.rows
+        k_blocks = (self.k + 63) // 64
+        tiles = (self.n_out + 127) // 128
+        self.decode_splits = max(1, min(N_SMS // tiles, 8, k_blocks // 8))
+
+    # ---- [n, in] -> [n, out] ----
+    def forward(self, x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        t = x.shape[0]
+        out = torch.empty((t, self.n_out), dtype=out_dtype, device=x.device)
+        if t == 0:
+            return out
+        self._run(x, out, splits=1)
+        return out
+
+    def forward_delta(self, x: torch.Tensor) -> torch.Tensor:
+        t = x.shape[0]
+        if self.gated:
+            raise KernelError("gemm_tc: a gated pair has no partial sums")
+        splits = self.decode_splits if t <= SMALL else 1
+        out = torch.empty((splits, t, self.n_out), dtype=torch.float32, device=x.device)
+        if t:
+            self._run(x, out, splits=splits)
+        return out
+
+    def _run(self, x: torch.Tensor, out: torch.Tensor, splits: int) -> None:
+        t = x.shape[0]
+        if t <= SMALL:
+            gemm_tc(self.w, self.n_out, x, t, bn=_ceil16(t), out=out, ldo=self.n_out,
+                    gated=1 if self.gated else 0, pair_offset=self.n_out, transposed=True, splits=splits,
+                    split_stride=t * self.n_out, max_smem=100 * 1024)
+        else:
+            bn = min(128 if self.gated else 256, _ceil16(self.n_out))
+            gemm_tc(x, t, self.w, self.n_out, bn=bn, out=out, ldo=self.n_out, gated=2 if self.gated else 0,
+                    pair_offset=self.n_out, transposed=False, splits=splits, split_stride=t * self.n_out,
+                    max_smem=200 * 1024)
+
+
+def plan_for(weight: torch.Tensor, gated: bool = False) -> Optional[Plan]:
+    """A plan for this weight, or None where the kernel does not take its sizes."""
+    if weight.dtype != torch.bfloat16 or not weight.is_cuda or weight.dim() != 2:
+        return None
+    if weight.shape[1] % 8 != 0 or weight.data_ptr() % 16 != 0:
+        return None
+    if gated and weight.shape[0] % 2 != 0:
+        return None
+    return Plan(weight, gated)
