@@ -148,7 +148,10 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--skip-points", action="store_true", help="no batch 1 / 64 runs")
+    ap.add_argument("--skip-e2e", action="store_true", help="no run through the Python entry point")
+    ap.add_argument("--skip-prefill", action="store_true")
+    ap.add_argument("--eager", action="store_true", help="no CUDA graphs (every kernel is a launch of its own)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -173,7 +176,8 @@ def main() -> int:
     per_seq = (PROMPT + 3 + steps + 64 + 63) // 64 * 64
     max_tokens = max(max_batch * per_seq, PREFILL + 64)
     t0 = time.time()
-    eng = wick.Engine.from_config(cfg, seed=0, dtype="bfloat16", max_tokens=max_tokens)
+    eng = wick.Engine.from_config(cfg, seed=0, dtype="bfloat16", max_tokens=max_tokens,
+                                  use_graphs=False if args.eager else None)
     torch.cuda.synchronize()
     load_s = time.time() - t0
     vocab = cfg.vocab_size
@@ -188,15 +192,17 @@ def main() -> int:
     achieved = step_bytes / (ms * 1e-3) / 1e9
 
     # ---- decode through the Python entry point, host tokens in and out ----
+    e2e_value = None
     g = torch.Generator().manual_seed(2)
     prompts = [torch.randint(0, vocab, (PROMPT,), generator=g).tolist() for _ in range(args.batch)]
     opts = wick.GenOptions(max_tokens=steps + 1, sampler=wick.SamplerConfig.greedy(), context=CONTEXT,
                            max_batch=args.batch)
-    wick.generate(eng, [p[:16] for p in prompts], wick.GenOptions(max_tokens=4, sampler=wick.SamplerConfig.greedy(),
-                                                                  context=CONTEXT, max_batch=args.batch))
-    res = wick.generate(eng, prompts, opts)
-    gen_ms = max(r.gen_ms for r in res)
-    e2e_value = sum(len(r.tokens) - 1 for r in res) / (gen_ms * 1e-3)
+    if not args.skip_e2e:
+        wick.generate(eng, [p[:16] for p in prompts], wick.GenOptions(max_tokens=4, sampler=wick.SamplerConfig.greedy(),
+                                                                      context=CONTEXT, max_batch=args.batch))
+        res = wick.generate(eng, prompts, opts)
+        gen_ms = max(r.gen_ms for r in res)
+        e2e_value = sum(len(r.tokens) - 1 for r in res) / (gen_ms * 1e-3)
     from wick_b200.engine.batch import BatchLayout
     h2d = BatchLayout(args.batch, args.batch, 16, args.batch, args.batch).size * 4
     d2h = args.batch * 4
@@ -205,7 +211,7 @@ def main() -> int:
     g = torch.Generator().manual_seed(3)
     ptoks = torch.randint(0, vocab, (PREFILL,), generator=g).tolist()
     times = []
-    for i in range(2 + 3):
+    for i in range(0 if args.skip_prefill else 2 + 3):
         s = eng.open_seq()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -216,7 +222,7 @@ def main() -> int:
         eng.close_seq(s)
         if i >= 2:
             times.append(e0.elapsed_time(e1))
-    pms = statistics.median(times)
+    pms = statistics.median(times) if times else float("nan")
     c = cfg
     gemm_params = len(eng.spec.schedule) * (c.hidden_size * (2 * c.q_dim + 2 * c.kv_dim) + 3 * c.hidden_size * c.intermediate_size)
     flops = 2.0 * PREFILL * gemm_params + 2.0 * vocab * c.hidden_size            # head on one row

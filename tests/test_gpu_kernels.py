@@ -148,10 +148,22 @@ def test_qk_norm_rope_append_and_attention(ops, dtype, heads, kv_heads, hd):
     # decode attention: the last token of each sequence alone
     fd = FakeBatch([1, 1], [t - 1 for t in totals], pages).sb
     last = torch.tensor([q_lens[0] - 1, sum(q_lens) - 1], device="cuda")
-    scratch = torch.empty(ops.attention_decode_scratch_floats(2, heads, hd, fd.max_kv_len), device="cuda")
-    outd = ops.attention_decode(q[last].contiguous(), kv, fd, 1 / math.sqrt(hd), scratch)
-    assert torch.isfinite(outd.float()).all()
-    assert (outd.float().cpu() - ref_o[last.cpu()]).abs().max() < tol(dtype, 2)
+    for plain in (False, True):
+        scratch = torch.full((ops.attention_decode_scratch_floats(2, heads, hd, fd.max_kv_len, dtype, plain),),
+                             float("nan"), device="cuda")
+        outd = ops.attention_decode(q[last].contiguous(), kv, fd, 1 / math.sqrt(hd), scratch, plain=plain)
+        assert torch.isfinite(outd.float()).all()
+        assert (outd.float().cpu() - ref_o[last.cpu()]).abs().max() < tol(dtype, 2)
+    ops.check_status()
+    # the projection output as float32 partial sums gives the same q and cache
+    parts = torch.stack([new.float() * 0.25, new.float() * 0.5, new.float() * 0.25])
+    kv2 = _paged(12, kv_heads, hd, dtype)
+    q2 = ops.qk_norm_rope_append(dev(parts), heads, kv_heads, hd, q_weight=dev(qw), k_weight=dev(kw), eps=eps,
+                                 cos=cos, sin=sin, kv=kv2, page_table=fb.page_table, seq_of_token=fb.seq_of_token,
+                                 positions=fb.positions, dtype=dtype)
+    assert (q2.float() - q.float()).abs().max() < tol(dtype, 4)
+    page = pages[1][0]
+    assert (kv2[page, :, :, :3].float() - kv[page, :, :, :3].float()).abs().max() < tol(dtype, 4)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -174,10 +186,11 @@ def test_attention_finds_one_far_key_among_hundreds(ops, dtype):
             kv[pages[0][p // 64], 0, :, p % 64] = k[p].to(dtype).cuda()
             kv[pages[0][p // 64], 1, :, p % 64] = v[p].to(dtype).cuda()
         fd = FakeBatch([1], [n - 1], pages).sb
-        scratch = torch.empty(ops.attention_decode_scratch_floats(1, heads, hd, n), device="cuda")
-        out = ops.attention_decode(dev(q.to(dtype)), kv, fd, 1 / math.sqrt(hd), scratch).float().cpu()
         want = v[far].to(dtype).float().repeat_interleave(heads // kv_heads, 0)
-        assert (out[0] - want).abs().max() < 1e-2, f"decode kernel missed key {far}"
+        for plain in (False, True):
+            scratch = torch.empty(ops.attention_decode_scratch_floats(1, heads, hd, n, dtype, plain), device="cuda")
+            out = ops.attention_decode(dev(q.to(dtype)), kv, fd, 1 / math.sqrt(hd), scratch, plain=plain).float().cpu()
+            assert (out[0] - want).abs().max() < 1e-2, f"decode kernel (plain={plain}) missed key {far}"
         # the same through the prompt kernel: 5 new tokens whose last one carries the query
         qs = torch.zeros(5, heads, hd)
         qs[4] = q[0]

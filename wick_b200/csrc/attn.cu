@@ -397,7 +397,7 @@ using namespace wick;
 typedef __nv_bfloat16 bf16;
 
 WICK_API int wick_attn_head_dim() { return HD; }
-WICK_API int wick_attn_decode_split() { return SPLIT; }
+WICK_API int wick_attn_decode_plain_split() { return SPLIT; }
 
 // q, out: [n_tokens, n_heads, HD]; kv: one schedule entry's cache.
 WICK_API int wick_attn_prompt_bf16(const void* q, const void* kv, void* out, const int* tile_seq, const int* tile_q0,
@@ -413,13 +413,13 @@ WICK_API int wick_attn_prompt_f32(const void* q, const void* kv, void* out, cons
                               n_heads, n_kv, scale, (cudaStream_t)s);
 }
 // scratch: float32 [scratch_floats], at least n_seqs*n_heads*ceil(max_kv_len/256)*(HD+2).
-WICK_API int wick_attn_decode_bf16(const void* q, const void* kv, void* out, float* scratch, int64_t scratch_floats,
+WICK_API int wick_attn_decode_plain_bf16(const void* q, const void* kv, void* out, float* scratch, int64_t scratch_floats,
                                    const int* kv_len, int n_seqs, int max_kv_len, const int* page_table,
                                    int table_width, int n_heads, int n_kv, float scale, void* s) {
     return attn_decode<bf16>(q, kv, out, scratch, nullptr, scratch_floats, kv_len, n_seqs, max_kv_len, page_table,
                              table_width, n_heads, n_kv, scale, (cudaStream_t)s);
 }
-WICK_API int wick_attn_decode_f32(const void* q, const void* kv, void* out, float* scratch, int64_t scratch_floats,
+WICK_API int wick_attn_decode_plain_f32(const void* q, const void* kv, void* out, float* scratch, int64_t scratch_floats,
                                   const int* kv_len, int n_seqs, int max_kv_len, const int* page_table,
                                   int table_width, int n_heads, int n_kv, float scale, void* s) {
     return attn_decode<float>(q, kv, out, scratch, nullptr, scratch_floats, kv_len, n_seqs, max_kv_len, page_table,

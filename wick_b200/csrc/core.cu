@@ -39,19 +39,46 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
     const int64_t r = rows ? rows[i] : i;
     float* xr = x + r * width;
     float ss = 0.f;
-    for (int j = threadIdx.x; j < width; j += blockDim.x) {
-        float v = xr[j];
-        if (delta) {
-            for (int s = 0; s < splits; ++s) v += delta[s * split_stride + r * width + j];
-            xr[j] = v;
+    if ((width & 3) == 0) {
+        // four floats per thread and iteration; all loads of an iteration are independent
+        for (int j = threadIdx.x * 4; j < width; j += blockDim.x * 4) {
+            float4 v = *reinterpret_cast<const float4*>(xr + j);
+            if (delta) {
+                for (int s = 0; s < splits; ++s) {
+                    const float4 d = *reinterpret_cast<const float4*>(delta + s * split_stride + r * width + j);
+                    v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+                }
+                *reinterpret_cast<float4*>(xr + j) = v;
+            }
+            *reinterpret_cast<float4*>(row + j) = v;
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
         }
-        row[j] = v;
-        ss += v * v;
+    } else {
+        for (int j = threadIdx.x; j < width; j += blockDim.x) {
+            float v = xr[j];
+            if (delta) {
+                for (int s = 0; s < splits; ++s) v += delta[s * split_stride + r * width + j];
+                xr[j] = v;
+            }
+            row[j] = v;
+            ss += v * v;
+        }
     }
     ss = block_sum(ss, red);
     const float scale = 1.0f / sqrtf(ss / (float)width + eps);
     TOut* o = out + (int64_t)i * width;
-    for (int j = threadIdx.x; j < width; j += blockDim.x) st(o + j, (row[j] * scale) * w[j]);
+    if ((width & 3) == 0) {
+        for (int j = threadIdx.x * 4; j < width; j += blockDim.x * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(row + j);
+            const float4 g = *reinterpret_cast<const float4*>(w + j);
+            st(o + j, (v.x * scale) * g.x);
+            st(o + j + 1, (v.y * scale) * g.y);
+            st(o + j + 2, (v.z * scale) * g.z);
+            st(o + j + 3, (v.w * scale) * g.w);
+        }
+    } else {
+        for (int j = threadIdx.x; j < width; j += blockDim.x) st(o + j, (row[j] * scale) * w[j]);
+    }
 }
 
 // x[r] += sum of delta for every row (no norm): resolves a pending residual.
@@ -83,7 +110,8 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const float
 // token's place in its sequence's cache page.
 template <typename T>
 __global__ void qk_norm_rope_append_kernel(
-    const T* __restrict__ qkv, int n_tokens, int n_heads, int n_kv, int hd,
+    const T* __restrict__ qkv, const float* __restrict__ parts, int splits, int64_t split_stride,
+    int n_tokens, int n_heads, int n_kv, int hd,
     const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
     const float* __restrict__ cos_t, const float* __restrict__ sin_t,
     T* __restrict__ q_out, T* __restrict__ kv, const int* __restrict__ page_table, int table_width,
@@ -95,7 +123,17 @@ __global__ void qk_norm_rope_append_kernel(
     const int t = item / heads_total, h = item % heads_total;
     const int half = hd >> 1;
     const int row_width = (n_heads + 2 * n_kv) * hd;
-    const T* src = qkv + (int64_t)t * row_width + (int64_t)h * hd;
+    // The projection output comes either as one array of T or as float32 partial
+    // sums [splits][tokens][row_width] that are added here, in index order.
+    const int64_t base = (int64_t)t * row_width + (int64_t)h * hd;
+    auto val = [&](int i) -> float {
+        if (parts) {
+            float v = parts[base + i];
+            for (int sp = 1; sp < splits; ++sp) v += parts[sp * split_stride + base + i];
+            return v;
+        }
+        return ld(qkv + base + i);
+    };
 
     T* dst;
     const float* w = nullptr;
@@ -112,13 +150,13 @@ __global__ void qk_norm_rope_append_kernel(
         w = is_v ? nullptr : k_w;
         rotate = !is_v;
         if (is_v) {
-            for (int i = lane; i < hd; i += 32) dst[i] = src[i];
+            for (int i = lane; i < hd; i += 32) st(dst + i, val(i));
             return;
         }
     }
     float ss = 0.f;
     for (int i = lane; i < hd; i += 32) {
-        const float v = ld(src + i);
+        const float v = val(i);
         ss += v * v;
     }
     float scale = 1.f;
@@ -127,7 +165,7 @@ __global__ void qk_norm_rope_append_kernel(
         scale = 1.0f / sqrtf(ss / (float)hd + eps);
     }
     for (int i = lane; i < half; i += 32) {
-        float a = ld(src + i), b = ld(src + i + half);
+        float a = val(i), b = val(i + half);
         if (w) {
             a = (a * scale) * w[i];
             b = (b * scale) * w[i + half];
@@ -220,7 +258,7 @@ WICK_API int wick_rope_table(const int* positions, const float* inv_freq, float*
 }
 
 template <typename T>
-static int qk_norm_rope_append(const void* qkv, int n_tokens, int n_heads, int n_kv, int hd, const float* q_w,
+static int qk_norm_rope_append(const void* qkv, const float* parts, int splits, int n_tokens, int n_heads, int n_kv, int hd, const float* q_w,
                                const float* k_w, float eps, const float* cos_t, const float* sin_t, void* q_out,
                                void* kv, const int* page_table, int table_width, const int* seq_of_token,
                                const int* positions, int write_kv, cudaStream_t s) {
@@ -230,25 +268,25 @@ static int qk_norm_rope_append(const void* qkv, int n_tokens, int n_heads, int n
     const int heads_total = n_heads + (write_kv ? 2 * n_kv : 0);
     const int warps = 4;
     qk_norm_rope_append_kernel<T><<<ceil_div((int64_t)n_tokens * heads_total, warps), warps * 32, 0, s>>>(
-        (const T*)qkv, n_tokens, n_heads, n_kv, hd, q_w, k_w, eps, cos_t, sin_t, (T*)q_out, (T*)kv, page_table,
-        table_width, seq_of_token, positions, write_kv);
+        (const T*)qkv, parts, splits, (int64_t)n_tokens * (n_heads + 2 * n_kv) * hd, n_tokens, n_heads, n_kv, hd, q_w,
+        k_w, eps, cos_t, sin_t, (T*)q_out, (T*)kv, page_table, table_width, seq_of_token, positions, write_kv);
     return check_launch("qk_norm_rope_append");
 }
 
-WICK_API int wick_qk_norm_rope_append_bf16(const void* qkv, int n_tokens, int n_heads, int n_kv, int hd,
+WICK_API int wick_qk_norm_rope_append_bf16(const void* qkv, const float* parts, int splits, int n_tokens, int n_heads, int n_kv, int hd,
                                            const float* q_w, const float* k_w, float eps, const float* cos_t,
                                            const float* sin_t, void* q_out, void* kv, const int* page_table,
                                            int table_width, const int* seq_of_token, const int* positions,
                                            int write_kv, void* s) {
-    return qk_norm_rope_append<bf16>(qkv, n_tokens, n_heads, n_kv, hd, q_w, k_w, eps, cos_t, sin_t, q_out, kv,
+    return qk_norm_rope_append<bf16>(qkv, parts, splits, n_tokens, n_heads, n_kv, hd, q_w, k_w, eps, cos_t, sin_t, q_out, kv,
                                      page_table, table_width, seq_of_token, positions, write_kv, (cudaStream_t)s);
 }
-WICK_API int wick_qk_norm_rope_append_f32(const void* qkv, int n_tokens, int n_heads, int n_kv, int hd,
+WICK_API int wick_qk_norm_rope_append_f32(const void* qkv, const float* parts, int splits, int n_tokens, int n_heads, int n_kv, int hd,
                                           const float* q_w, const float* k_w, float eps, const float* cos_t,
                                           const float* sin_t, void* q_out, void* kv, const int* page_table,
                                           int table_width, const int* seq_of_token, const int* positions,
                                           int write_kv, void* s) {
-    return qk_norm_rope_append<float>(qkv, n_tokens, n_heads, n_kv, hd, q_w, k_w, eps, cos_t, sin_t, q_out, kv,
+    return qk_norm_rope_append<float>(qkv, parts, splits, n_tokens, n_heads, n_kv, hd, q_w, k_w, eps, cos_t, sin_t, q_out, kv,
                                       page_table, table_width, seq_of_token, positions, write_kv, (cudaStream_t)s);
 }
 

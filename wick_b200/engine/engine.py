@@ -138,9 +138,7 @@ class Engine:
         """Raise if a kernel reported that it gave up a bounded wait (this
         synchronises the device, so it runs only now and then)."""
         self._steps_since_check = 0
-        if self.dtype == torch.bfloat16:
-            from ..ops import gemm_tc
-            gemm_tc.check_status()
+        ops.check_status()
 
     # ---- sequences ---------------------------------------------------------
     def open_seq(self) -> int:

@@ -92,8 +92,33 @@ def _attn(head_dim: int) -> _Lib:
         if head_dim % 16 != 0 or not 16 <= head_dim <= 256:
             raise KernelError(f"attention kernels take a head_dim that is a multiple of 16 between 16 and 256, "
                               f"not {head_dim}")
-        lib = _libs[key] = _Lib(f"wick_attn_hd{head_dim}", ["attn.cu"], [f"WICK_HD={head_dim}"])
+        lib = _libs[key] = _Lib(f"wick_attn_hd{head_dim}", ["attn.cu", "attn_decode.cu"], [f"WICK_HD={head_dim}"])
     return lib
+
+
+# One device word that kernels with bounded waits write a code to when a wait
+# gives up: 1-3 the tensor-core matrix product (a free stage, a TMA copy, the
+# accumulator), 4 decode attention (its bulk copies).
+_status: Optional[torch.Tensor] = None
+_STATUS_TEXT = {1: "gemm_tc: a free shared-memory stage", 2: "gemm_tc: a TMA copy", 3: "gemm_tc: the accumulator",
+                4: "attention decode: its bulk copies"}
+
+
+def status_tensor(device) -> torch.Tensor:
+    global _status
+    if _status is None or _status.device != torch.device(device):
+        _status = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status
+
+
+def check_status() -> None:
+    """Raise if a kernel gave up a bounded wait (this synchronises the device)."""
+    if _status is not None:
+        code = int(_status.item())
+        if code != 0:
+            _status.zero_()
+            raise KernelError(f"a kernel gave up waiting for {_STATUS_TEXT.get(code, 'code %d' % code)}; "
+                              f"its output is invalid")
 
 
 def _p(t: Optional[torch.Tensor]):
@@ -185,14 +210,24 @@ def qk_norm_rope_append(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: in
                         q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
                         cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], kv: Optional[torch.Tensor],
                         page_table: torch.Tensor, seq_of_token: torch.Tensor, positions: torch.Tensor,
-                        write_kv: bool = True, q_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                        write_kv: bool = True, q_out: Optional[torch.Tensor] = None,
+                        dtype: Optional[torch.dtype] = None) -> torch.Tensor:
     """Per-head RMS norm of q and k (if weights are given), half-split rotation
     (if tables are given), then q -> ``q_out`` [n, n_heads, head_dim] and k, v ->
-    the cache ``kv`` [pages, 2, n_kv, 64, head_dim] at each token's position."""
+    the cache ``kv`` [pages, 2, n_kv, 64, head_dim] at each token's position.
+
+    qkv: [n, (n_heads + 2 n_kv) head_dim] in the activation dtype, or float32
+    partial sums [splits, n, ...] (then ``dtype`` names the activation dtype)."""
     _cuda("qkv", qkv)
-    n = qkv.shape[0]
-    _need(qkv.dim() == 2 and qkv.shape[1] == (n_heads + 2 * n_kv) * head_dim,
-          f"qkv must be [n, {(n_heads + 2 * n_kv) * head_dim}], is {tuple(qkv.shape)}")
+    width = (n_heads + 2 * n_kv) * head_dim
+    parts = qkv.dim() == 3
+    if parts:
+        _need(qkv.dtype == torch.float32 and qkv.shape[2] == width and dtype is not None,
+              f"partial sums must be float32 [splits, n, {width}] and come with the activation dtype")
+        n, splits, act = qkv.shape[1], qkv.shape[0], dtype
+    else:
+        _need(qkv.dim() == 2 and qkv.shape[1] == width, f"qkv must be [n, {width}], is {tuple(qkv.shape)}")
+        n, splits, act = qkv.shape[0], 0, qkv.dtype
     for nm, w in (("q_weight", q_weight), ("k_weight", k_weight)):
         if w is not None:
             _cuda(nm, w, torch.float32, (head_dim,))
@@ -201,19 +236,20 @@ def qk_norm_rope_append(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: in
         _cuda("cos", cos, torch.float32, (n, head_dim // 2))
         _cuda("sin", sin, torch.float32, (n, head_dim // 2))
     if write_kv:
-        _cuda("kv", kv, qkv.dtype)
+        _cuda("kv", kv, act)
         _need(kv.dim() == 5 and tuple(kv.shape[1:]) == (2, n_kv, PAGE, head_dim),
               f"kv must be [pages, 2, {n_kv}, {PAGE}, {head_dim}], is {tuple(kv.shape)}")
     _cuda("page_table", page_table, torch.int32)
     _cuda("seq_of_token", seq_of_token, torch.int32, (n,))
     _cuda("positions", positions, torch.int32, (n,))
     if q_out is None:
-        q_out = torch.empty((n, n_heads, head_dim), dtype=qkv.dtype, device=qkv.device)
-    _cuda("q_out", q_out, qkv.dtype, (n, n_heads, head_dim))
-    _core().call(f"wick_qk_norm_rope_append_{_dt(qkv)}", "piiiippfpppppippip",
-                 _p(qkv), n, n_heads, n_kv, head_dim, _p(q_weight), _p(k_weight), float(eps), _p(cos), _p(sin),
-                 _p(q_out), _p(kv) if write_kv else None, _p(page_table), page_table.shape[-1], _p(seq_of_token),
-                 _p(positions), 1 if write_kv else 0, _stream())
+        q_out = torch.empty((n, n_heads, head_dim), dtype=act, device=qkv.device)
+    _cuda("q_out", q_out, act, (n, n_heads, head_dim))
+    _core().call(f"wick_qk_norm_rope_append_{_dt(q_out)}", "ppiiiiippfpppppippip",
+                 None if parts else _p(qkv), _p(qkv) if parts else None, splits, n, n_heads, n_kv, head_dim,
+                 _p(q_weight), _p(k_weight), float(eps), _p(cos), _p(sin), _p(q_out), _p(kv) if write_kv else None,
+                 _p(page_table), page_table.shape[-1], _p(seq_of_token), _p(positions), 1 if write_kv else 0,
+                 _stream())
     return q_out
 
 
@@ -269,15 +305,37 @@ def attention_prompt(q: torch.Tensor, kv: torch.Tensor, batch, scale: float,
     return out
 
 
-def attention_decode_scratch_floats(n_seqs: int, n_heads: int, head_dim: int, max_kv_len: int) -> int:
-    return n_seqs * n_heads * max(1, -(-max_kv_len // DECODE_SPLIT)) * (head_dim + 2)
+_decode_split: Dict[tuple, int] = {}
+
+
+def attention_decode_split(head_dim: int, dtype: torch.dtype, plain: bool = False) -> int:
+    """Cached positions handled by one block of the decode kernel."""
+    key = (head_dim, dtype, plain)
+    v = _decode_split.get(key)
+    if v is None:
+        lib = _attn(head_dim)._lib
+        name = "wick_attn_decode_plain_split" if plain else \
+            f"wick_attn_decode_split_{'bf16' if dtype == torch.bfloat16 else 'f32'}"
+        f = getattr(lib, name)
+        f.restype = ctypes.c_int
+        f.argtypes = []
+        v = _decode_split[key] = int(f())
+    return v
+
+
+def attention_decode_scratch_floats(n_seqs: int, n_heads: int, head_dim: int, max_kv_len: int,
+                                    dtype: torch.dtype = torch.bfloat16, plain: bool = False) -> int:
+    split = attention_decode_split(head_dim, dtype, plain)
+    return n_seqs * n_heads * max(1, -(-max_kv_len // split)) * (head_dim + 2)
 
 
 def attention_decode(q: torch.Tensor, kv: torch.Tensor, batch, scale: float, scratch: torch.Tensor,
-                     out: Optional[torch.Tensor] = None, max_kv_len: Optional[int] = None) -> torch.Tensor:
+                     out: Optional[torch.Tensor] = None, max_kv_len: Optional[int] = None,
+                     plain: bool = False) -> torch.Tensor:
     """One new token per sequence.  scratch: float32, at least
     :func:`attention_decode_scratch_floats` elements; it holds the per-split
-    partial sums between the two kernels."""
+    partial sums between the two kernels.  plain: the form without shared-memory
+    staging (the fast form's twin)."""
     _cuda("q", q)
     n, n_heads, hd = q.shape
     _cuda("kv", kv, q.dtype)
@@ -290,9 +348,15 @@ def attention_decode(q: torch.Tensor, kv: torch.Tensor, batch, scale: float, scr
         out = torch.empty_like(q)
     _cuda("out", out, q.dtype, q.shape)
     mk = batch.max_kv_len if max_kv_len is None else max_kv_len
-    _attn(hd).call(f"wick_attn_decode_{_dt(q)}", "pppplpiipiiifp", _p(q), _p(kv), _p(out),
-                   _p(scratch), scratch.numel(), _p(batch.kv_len), n, mk, _p(batch.page_table), batch.table_width,
-                   n_heads, n_kv, float(scale), _stream(), kernels=2)
+    if plain:
+        _attn(hd).call(f"wick_attn_decode_plain_{_dt(q)}", "pppplpiipiiifp", _p(q), _p(kv), _p(out),
+                       _p(scratch), scratch.numel(), _p(batch.kv_len), n, mk, _p(batch.page_table),
+                       batch.table_width, n_heads, n_kv, float(scale), _stream(), kernels=2)
+    else:
+        _attn(hd).call(f"wick_attn_decode_{_dt(q)}", "pppplpiipiiifpp", _p(q), _p(kv), _p(out),
+                       _p(scratch), scratch.numel(), _p(batch.kv_len), n, mk, _p(batch.page_table),
+                       batch.table_width, n_heads, n_kv, float(scale), _p(status_tensor(q.device)), _stream(),
+                       kernels=2)
     return out
 
 

@@ -138,6 +138,15 @@ def compile_library(name: str, sources: Sequence[str], defines: Sequence[str] = 
                     pass
                 raise BuildError(f"nvcc failed for {name} (exit {proc.returncode}):\n{' '.join(cmd)}\n{log}")
             os.replace(tmp, out)
+            # earlier builds of the same library (other source or flag hashes) are of no use any more
+            prefix = f"{name}-"
+            for f in os.listdir(os.path.dirname(out)):
+                if f.startswith(prefix) and f.endswith(".so") and f != os.path.basename(out) \
+                        and len(f) == len(os.path.basename(out)):
+                    try:
+                        os.remove(os.path.join(os.path.dirname(out), f))
+                    except OSError:
+                        pass
             if verbose:
                 _note(f"compiled {name} in {time.time() - t0:.0f} s -> {out}")
             return out

@@ -21,36 +21,16 @@ from typing import Optional
 
 import torch
 
-from . import KernelError, _Lib, _libs, _p, _stream, launches  # noqa: F401
+from . import KernelError, _Lib, _libs, _p, _stream, check_status, status_tensor  # noqa: F401
 
 SMALL = 64                  # up to this many tokens the weights are the 128-row operand
 N_SMS = 148
-
-_status: Optional[torch.Tensor] = None
-
 
 def _lib() -> _Lib:
     lib = _libs.get("gemm_tc")
     if lib is None:
         lib = _libs["gemm_tc"] = _Lib("wick_gemm_tc", ["gemm_tc.cu"])
     return lib
-
-
-def status_tensor(device) -> torch.Tensor:
-    global _status
-    if _status is None or _status.device != device:
-        _status = torch.zeros(1, dtype=torch.int32, device=device)
-    return _status
-
-
-def check_status() -> None:
-    """Raise if a tensor-core kernel gave up waiting (synchronises the device)."""
-    if _status is not None:
-        code = int(_status.item())
-        if code != 0:
-            _status.zero_()
-            what = {1: "a free shared-memory stage", 2: "a TMA copy", 3: "the accumulator"}.get(code, "?")
-            raise KernelError(f"gemm_tc: a kernel gave up waiting for {what} (code {code}); its output is invalid")
 
 
 _SIG = "plipliiiiiiiplilipp"
@@ -111,7 +91,7 @@ class Plan:
         if t <= SMALL:
             gemm_tc(self.w, self.n_out, x, t, bn=_ceil16(t), out=out, ldo=self.n_out,
                     gated=1 if self.gated else 0, pair_offset=self.n_out, transposed=True, splits=splits,
-                    split_stride=t * self.n_out, max_smem=100 * 1024)
+                    split_stride=t * self.n_out, max_smem=200 * 1024)
         else:
             bn = min(128 if self.gated else 256, _ceil16(self.n_out))
             gemm_tc(x, t, self.w, self.n_out, bn=bn, out=out, ldo=self.n_out, gated=2 if self.gated else 0,

@@ -153,7 +153,7 @@ class GQAttention(Mixer):
         return self.qkv.weight_bytes() + self.o.weight_bytes() + (2 * self.head_dim * 4 if self.q_norm else 0)
 
     def forward(self, x, batch, cache, write_cache):
-        qkv = self.qkv.forward(x, self.ctx.dtype)                       # [n, q_dim + 2 kv_dim]
+        qkv = self.qkv.forward_delta(x)                  # float32 partial sums [splits, n, q_dim + 2 kv_dim]
         inv_freq = self.position.rotary_inv_freq()
         cos = sin = None
         if inv_freq is not None:
@@ -164,12 +164,14 @@ class GQAttention(Mixer):
             k_weight=self.k_norm.weight if self.k_norm else None,
             eps=self.q_norm.eps if self.q_norm else 0.0,
             cos=cos, sin=sin, kv=cache.kv, page_table=batch.page_table,
-            seq_of_token=batch.seq_of_token, positions=batch.positions, write_kv=write_cache)
+            seq_of_token=batch.seq_of_token, positions=batch.positions, write_kv=write_cache,
+            dtype=self.ctx.dtype)
         if inv_freq is None and not isinstance(self.position, NoPosition):
             raise NotImplementedError("a position encoding that is not a half-split rotation has to be applied "
                                       "before the cache append; give the mixer a kernel for it")
         if batch.is_decode:
-            need = ops.attention_decode_scratch_floats(batch.n_seqs, self.heads, self.head_dim, batch.kv_bound)
+            need = ops.attention_decode_scratch_floats(batch.n_seqs, self.heads, self.head_dim, batch.kv_bound,
+                                                       self.ctx.dtype)
             att = ops.attention_decode(q, cache.kv, batch, self.scale,
                                        batch.workspace.get("attention_decode", need, torch.float32),
                                        max_kv_len=batch.kv_bound)
