@@ -296,3 +296,69 @@ WICK_API int wick_attn_decode_f32(const void* q, const void* kv, void* out, floa
     return fastdecode::run<float>(q, kv, out, scratch, scratch_floats, kv_len, n_seqs, max_kv_len, page_table, table_width,
                                   n_heads, n_kv, scale, status, (cudaStream_t)s);
 }
+
+// ---------------------------------------------------------------------------
+// Decode attention for callers that cannot allocate device memory (declared in
+// attn_decode_noalloc.h; wick has nothing like it).
+//
+// wick_attn_decode_bf16 above needs a scratch buffer from its caller for the
+// per-split partial results.  A host that has no allocator to ask — a plug-in
+// inside another runtime's memory pool, a real-time loop that may not block in
+// cudaMalloc, a process whose memory budget is fixed at load time — can call
+// this entry point instead: the partial results go to a fixed array that is part
+// of this library's image on the device.
+//
+// * The array holds kNoAllocFloats float32 (8 MiB).  Every GPU that loads this
+//   library carries it until the process exits.  A call that needs more
+//   (n_seqs * n_heads * ceil(max_kv_len / split) * (head_dim + 2) floats) is
+//   refused with an error; nothing is launched.
+// * In host code the array's name is only a handle.  The device address is
+//   looked up with cudaGetSymbolAddress, once per device, by the first call made
+//   while that device is current; make that first call before capturing a stream.
+// * All calls share the one array, and it keeps what the last call left.  Nothing
+//   in it has to start at zero: every entry a call reads was written by that
+//   call.  Two calls that overlap on the GPU (different streams) race on it; keep
+//   calls that use this entry point on one stream or order them with events.
+// * No cudaMalloc, cudaFree or other allocating routine is called, here or below.
+namespace wick {
+namespace fastdecode {
+
+constexpr long long kNoAllocFloats = 2ll * 1024 * 1024;
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocFloats];
+
+static int noalloc_scratch(float** out) {
+    static float* per_device[64] = {};
+    int dev = -1;
+    WICK_CUDA(cudaGetDevice(&dev));
+    WICK_REQUIRE(dev >= 0 && dev < 64, "attention decode (no allocation): device index %d is out of range", dev);
+    if (per_device[dev] == nullptr) {
+        float* p = nullptr;
+        WICK_CUDA(cudaGetSymbolAddress((void**)&p, g_noalloc_scratch));
+        WICK_REQUIRE(p != nullptr, "attention decode (no allocation): the scratch array has no device address");
+        per_device[dev] = p;
+    }
+    *out = per_device[dev];
+    return 0;
+}
+
+}  // namespace fastdecode
+}  // namespace wick
+
+WICK_API long long wick_attn_decode_noalloc_capacity() { return wick::fastdecode::kNoAllocFloats; }
+
+WICK_API int wick_attn_decode_noalloc_bf16(const void* q, const void* kv, void* out, const int* kv_len, int n_seqs,
+                                           int max_kv_len, const int* page_table, int table_width, int n_heads,
+                                           int n_kv, float scale, int* status, void* s) {
+    using namespace wick::fastdecode;
+    WICK_REQUIRE(n_seqs >= 0 && n_heads > 0 && max_kv_len >= 0, "attention decode (no allocation): bad sizes");
+    const long long splits = (max_kv_len > 0 ? max_kv_len : 1) / Shape<bf16>::SPLIT +
+                             ((max_kv_len > 0 ? max_kv_len : 1) % Shape<bf16>::SPLIT != 0);
+    const long long need = (long long)n_seqs * n_heads * splits * (HD + 2);
+    WICK_REQUIRE(need <= kNoAllocFloats,
+                 "attention decode (no allocation): %d sequences x %d heads x %lld splits need %lld floats of scratch, "
+                 "the built-in array holds %lld", n_seqs, n_heads, splits, need, kNoAllocFloats);
+    float* scratch = nullptr;
+    if (int e = noalloc_scratch(&scratch)) return e;
+    return run<bf16>(q, kv, out, scratch, kNoAllocFloats, kv_len, n_seqs, max_kv_len, page_table, table_width, n_heads,
+                     n_kv, scale, status, (cudaStream_t)s);
+}
