@@ -136,6 +136,7 @@ def test_qk_norm_rope_append_and_attention(ops, dtype, heads, kv_heads, hd):
             assert torch.equal(kv[page, 1, :, p % 64].float().cpu(), refs[b][2][p].to(dtype).float())
     # prompt attention over prefix + new tokens
     out = ops.attention_prompt(q, kv, fb, 1 / math.sqrt(hd))
+    out_plain = ops.attention_prompt(q, kv, fb, 1 / math.sqrt(hd), plain=True)
     ref_o = []
     for b in range(2):
         qq, kk, vv = refs[b]
@@ -145,6 +146,7 @@ def test_qk_norm_rope_append_and_attention(ops, dtype, heads, kv_heads, hd):
     ref_o = torch.cat(ref_o)
     assert torch.isfinite(out.float()).all(), "a NaN from an unwritten cache position leaked"
     assert (out.float().cpu() - ref_o).abs().max() < tol(dtype, 2)
+    assert (out_plain.float().cpu() - ref_o).abs().max() < tol(dtype, 2), "the CUDA-core twin"
     # decode attention: the last token of each sequence alone
     fd = FakeBatch([1, 1], [t - 1 for t in totals], pages).sb
     last = torch.tensor([q_lens[0] - 1, sum(q_lens) - 1], device="cuda")

@@ -13,8 +13,9 @@ pytestmark = pytest.mark.gpu
 
 
 def _library(head_dim):
+    from wick_b200.ops import ATTN_SOURCES
     from wick_b200.ops.build import compile_library
-    path = compile_library(f"wick_attn_hd{head_dim}", ["attn.cu", "attn_decode.cu"], [f"WICK_HD={head_dim}"])
+    path = compile_library(f"wick_attn_hd{head_dim}", ATTN_SOURCES, [f"WICK_HD={head_dim}"])
     lib = ctypes.CDLL(path)
     P, I, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
     lib.wick_last_error.restype = ctypes.c_char_p

@@ -85,6 +85,9 @@ def _simt() -> _Lib:
     return lib
 
 
+ATTN_SOURCES = ["attn.cu", "attn_decode.cu", "attn_prompt_mma.cu"]
+
+
 def _attn(head_dim: int) -> _Lib:
     key = f"attn{head_dim}"
     lib = _libs.get(key)
@@ -92,7 +95,7 @@ def _attn(head_dim: int) -> _Lib:
         if head_dim % 16 != 0 or not 16 <= head_dim <= 256:
             raise KernelError(f"attention kernels take a head_dim that is a multiple of 16 between 16 and 256, "
                               f"not {head_dim}")
-        lib = _libs[key] = _Lib(f"wick_attn_hd{head_dim}", ["attn.cu", "attn_decode.cu"], [f"WICK_HD={head_dim}"])
+        lib = _libs[key] = _Lib(f"wick_attn_hd{head_dim}", ATTN_SOURCES, [f"WICK_HD={head_dim}"])
     return lib
 
 
@@ -286,9 +289,11 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, *, gated
 
 # ---------------------------------------------------------------------------
 def attention_prompt(q: torch.Tensor, kv: torch.Tensor, batch, scale: float,
-                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     out: Optional[torch.Tensor] = None, plain: bool = False) -> torch.Tensor:
     """Causal attention of the step's new tokens over the cache (which already
-    holds their keys and values).  q: [n, heads, d]; kv: [pages, 2, kv_heads, 64, d]."""
+    holds their keys and values).  q: [n, heads, d]; kv: [pages, 2, kv_heads, 64, d].
+    bfloat16 with a head size up to 128 runs on the tensor cores unless ``plain``
+    asks for the CUDA-core form (which is also the float32 kernel)."""
     _cuda("q", q)
     n, n_heads, hd = q.shape
     _cuda("kv", kv, q.dtype)
@@ -299,7 +304,9 @@ def attention_prompt(q: torch.Tensor, kv: torch.Tensor, batch, scale: float,
     if out is None:
         out = torch.empty_like(q)
     _cuda("out", out, q.dtype, q.shape)
-    _attn(hd).call(f"wick_attn_prompt_{_dt(q)}", "pppppipppiiifp", _p(q), _p(kv), _p(out), _p(batch.tile_seq),
+    fast = q.dtype == torch.bfloat16 and hd <= 128 and not plain
+    _attn(hd).call("wick_attn_prompt_mma_bf16" if fast else f"wick_attn_prompt_{_dt(q)}", "pppppipppiiifp",
+                   _p(q), _p(kv), _p(out), _p(batch.tile_seq),
                    _p(batch.tile_q0), batch.n_tiles, _p(batch.cu_seqlens), _p(batch.start), _p(batch.page_table),
                    batch.table_width, n_heads, n_kv, float(scale), _stream())
     return out

@@ -89,9 +89,13 @@ class Plan:
     def _run(self, x: torch.Tensor, out: torch.Tensor, splits: int) -> None:
         t = x.shape[0]
         if t <= SMALL:
+            # One block per SM with a deep ring when the blocks fit in one wave; two
+            # smaller ones per SM when there are several waves, so that one block's
+            # start and end overlap another's streaming.
+            blocks = (self.n_out + 127) // 128 * splits
             gemm_tc(self.w, self.n_out, x, t, bn=_ceil16(t), out=out, ldo=self.n_out,
                     gated=1 if self.gated else 0, pair_offset=self.n_out, transposed=True, splits=splits,
-                    split_stride=t * self.n_out, max_smem=200 * 1024)
+                    split_stride=t * self.n_out, max_smem=(200 if blocks <= N_SMS else 100) * 1024)
         else:
             bn = min(128 if self.gated else 256, _ceil16(self.n_out))
             gemm_tc(x, t, self.w, self.n_out, bn=bn, out=out, ldo=self.n_out, gated=2 if self.gated else 0,
