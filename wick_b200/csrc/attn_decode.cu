@@ -52,6 +52,8 @@ attn_decode_fast_kernel(const T* __restrict__ q, const T* __restrict__ kv, float
     using S = Shape<T>;
     constexpr int EPC = S::EPC, CHUNKS = S::CHUNKS, WARPS = S::WARPS, SPLIT = S::SPLIT, THREADS = S::THREADS;
     constexpr int TS = S::TS, CPL = S::CPL, KPI = S::KPI;
+    pdl_trigger();
+    pdl_wait();
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int kv_len = kv_len_arr[b];
     const int key_begin = split * SPLIT;
@@ -230,6 +232,8 @@ __global__ void attn_decode_fast_merge_kernel(const float* __restrict__ part_o, 
                                               const int* __restrict__ kv_len_arr, T* __restrict__ out, int n_heads,
                                               int max_splits) {
     constexpr int SPLIT = Shape<T>::SPLIT;
+    pdl_trigger();
+    pdl_wait();
     const int head = blockIdx.x, b = blockIdx.y;
     const int n_splits = (kv_len_arr[b] + SPLIT - 1) / SPLIT;
     const int64_t row0 = ((int64_t)b * n_heads + head) * max_splits;
@@ -263,11 +267,11 @@ int run(const void* q, const void* kv, void* out, float* scratch, int64_t scratc
         WICK_CUDA(cudaFuncSetAttribute(attn_decode_fast_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM));
         raised = true;
     }
-    attn_decode_fast_kernel<T><<<dim3(max_splits, n_kv, n_seqs), S::THREADS, S::SMEM, s>>>(
-        (const T*)q, (const T*)kv, scratch, ml, kv_len, page_table, table_width, n_heads, n_kv, max_splits, scale, status);
+    WICK_CUDA(launch(attn_decode_fast_kernel<T>, dim3(max_splits, n_kv, n_seqs), dim3(S::THREADS), S::SMEM, s, (const T*)q,
+                     (const T*)kv, scratch, ml, kv_len, page_table, table_width, n_heads, n_kv, max_splits, scale, status));
     if (int e = check_launch("attn_decode")) return e;
-    attn_decode_fast_merge_kernel<T><<<dim3(n_heads, n_seqs), HD >= 128 ? 128 : 64, 0, s>>>(scratch, ml, kv_len, (T*)out,
-                                                                                          n_heads, max_splits);
+    WICK_CUDA(launch(attn_decode_fast_merge_kernel<T>, dim3(n_heads, n_seqs), dim3(HD >= 128 ? 128 : 64), 0, s,
+                     (const float*)scratch, (const float*)ml, kv_len, (T*)out, n_heads, max_splits));
     return check_launch("attn_decode_merge");
 }
 

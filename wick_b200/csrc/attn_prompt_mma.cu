@@ -77,6 +77,8 @@ attn_prompt_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv, 
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);              // [64][HD]
     bf16* Ks = Qs + QT * HD;                                   // [2][64][HD]
     bf16* Vs = Ks + 2 * kPage * HD;                            // [2][64][HD]
+    pdl_trigger();
+    pdl_wait();
 
     const int tile = n_tiles - 1 - blockIdx.x;                 // long tiles (late rows of long prompts) first
     const int head = blockIdx.y;
@@ -263,8 +265,8 @@ WICK_API int wick_attn_prompt_mma_bf16(const void* q, const void* kv, void* out,
         WICK_CUDA(cudaFuncSetAttribute(attn_prompt_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         raised = true;
     }
-    attn_prompt_mma_kernel<<<dim3(n_tiles, n_heads), 128, smem, (cudaStream_t)s>>>(
-        (const bf16*)q, (const bf16*)kv, (bf16*)out, tile_seq, tile_q0, cu_seqlens, start, page_table, table_width,
-        n_tiles, n_heads, n_kv, scale);
+    WICK_CUDA(launch(attn_prompt_mma_kernel, dim3(n_tiles, n_heads), dim3(128), smem, (cudaStream_t)s, (const bf16*)q,
+                     (const bf16*)kv, (bf16*)out, tile_seq, tile_q0, cu_seqlens, start, page_table, table_width, n_tiles,
+                     n_heads, n_kv, scale));
     return check_launch("attn_prompt_mma");
 }

@@ -10,6 +10,7 @@
 #include <stdarg.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #define WICK_API extern "C" __attribute__((visibility("default")))
 
@@ -127,6 +128,42 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 }
 
 inline int ceil_div(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }
+
+// ---- programmatic dependent launch -------------------------------------------
+// Kernels are launched so that the next kernel in the stream may be scheduled
+// while this one still runs.  A kernel therefore (1) lets its successor start
+// (pdl_trigger) and (2) waits until its predecessor has completed and its writes
+// are visible (pdl_wait) before it touches anything another kernel produced or
+// may still read.  Only loads of data that no kernel ever writes (weights) may
+// come before pdl_wait.  Both are no-ops for a kernel launched the ordinary way.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+inline bool pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("WICK_B200_NO_PDL");
+        on = (e && e[0] && e[0] != '0') ? 0 : 1;
+    }
+    return on == 1;
+}
+
+// kernel<<<grid, block, smem, stream>>>(args...) with the programmatic
+// serialization attribute (unless WICK_B200_NO_PDL is set).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
 
 }  // namespace wick
 

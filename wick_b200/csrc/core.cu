@@ -18,6 +18,8 @@ constexpr int kPage = 64;
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
                              float* __restrict__ out, int width) {
+    pdl_trigger();
+    pdl_wait();
     const int64_t row = blockIdx.x;
     const T* src = table + (int64_t)tokens[row] * width;
     float* dst = out + row * width;
@@ -33,6 +35,8 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
                                int64_t split_stride, const float* __restrict__ w, float eps,
                                const int* __restrict__ rows, TOut* __restrict__ out, int width) {
     extern __shared__ float smem[];
+    pdl_trigger();
+    pdl_wait();
     float* row = smem;
     float* red = smem + width;
     const int i = blockIdx.x;
@@ -94,6 +98,8 @@ __global__ void add_delta_kernel(float* __restrict__ x, const float* __restrict_
 // ---- rotary tables ---------------------------------------------------------
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
                                   float* __restrict__ cos_t, float* __restrict__ sin_t, int n, int half) {
+    pdl_trigger();
+    pdl_wait();
     int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (int64_t)n * half) return;
     const int t = idx / half, i = idx % half;
@@ -116,6 +122,8 @@ __global__ void qk_norm_rope_append_kernel(
     const float* __restrict__ cos_t, const float* __restrict__ sin_t,
     T* __restrict__ q_out, T* __restrict__ kv, const int* __restrict__ page_table, int table_width,
     const int* __restrict__ seq_of_token, const int* __restrict__ positions, int write_kv) {
+    pdl_trigger();
+    pdl_wait();
     const int lane = threadIdx.x & 31;
     const int heads_total = n_heads + (write_kv ? 2 * n_kv : 0);
     const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -195,7 +203,7 @@ template <typename T>
 int embed(const void* table, const int* tokens, float* out, int n, int width, int64_t vocab, cudaStream_t s) {
     WICK_REQUIRE(n >= 0 && width > 0 && vocab > 0, "embed: bad sizes n=%d width=%d", n, width);
     if (n == 0) return 0;
-    embed_kernel<T><<<n, 256, 0, s>>>((const T*)table, tokens, out, width);
+    WICK_CUDA(launch(embed_kernel<T>, dim3(n), dim3(256), 0, s, (const T*)table, tokens, out, width));
     return check_launch("embed");
 }
 
@@ -213,8 +221,8 @@ int rmsnorm(float* x, const float* delta, int splits, int64_t n_rows_x, const fl
         raised = true;
     }
     const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
-    rmsnorm_kernel<TOut><<<n_out, threads, smem, s>>>(x, delta, splits, n_rows_x * width, w, eps, rows,
-                                                      (TOut*)out, width);
+    WICK_CUDA(launch(rmsnorm_kernel<TOut>, dim3(n_out), dim3(threads), smem, s, x, delta, splits, n_rows_x * width, w,
+                     eps, rows, (TOut*)out, width));
     return check_launch("rmsnorm");
 }
 
@@ -252,8 +260,8 @@ WICK_API int wick_add_delta(float* x, const float* delta, int splits, int64_t n,
 WICK_API int wick_rope_table(const int* positions, const float* inv_freq, float* cos_t, float* sin_t, int n,
                              int half, void* s) {
     if (n == 0 || half == 0) return 0;
-    rope_table_kernel<<<ceil_div((int64_t)n * half, 256), 256, 0, (cudaStream_t)s>>>(positions, inv_freq, cos_t,
-                                                                                     sin_t, n, half);
+    WICK_CUDA(launch(rope_table_kernel, dim3(ceil_div((int64_t)n * half, 256)), dim3(256), 0, (cudaStream_t)s, positions,
+                     inv_freq, cos_t, sin_t, n, half));
     return check_launch("rope_table");
 }
 
@@ -267,9 +275,10 @@ static int qk_norm_rope_append(const void* qkv, const float* parts, int splits, 
     if (n_tokens == 0) return 0;
     const int heads_total = n_heads + (write_kv ? 2 * n_kv : 0);
     const int warps = 4;
-    qk_norm_rope_append_kernel<T><<<ceil_div((int64_t)n_tokens * heads_total, warps), warps * 32, 0, s>>>(
-        (const T*)qkv, parts, splits, (int64_t)n_tokens * (n_heads + 2 * n_kv) * hd, n_tokens, n_heads, n_kv, hd, q_w,
-        k_w, eps, cos_t, sin_t, (T*)q_out, (T*)kv, page_table, table_width, seq_of_token, positions, write_kv);
+    WICK_CUDA(launch(qk_norm_rope_append_kernel<T>, dim3(ceil_div((int64_t)n_tokens * heads_total, warps)),
+                     dim3(warps * 32), 0, s, (const T*)qkv, parts, splits,
+                     (int64_t)n_tokens * (n_heads + 2 * n_kv) * hd, n_tokens, n_heads, n_kv, hd, q_w, k_w, eps, cos_t,
+                     sin_t, (T*)q_out, (T*)kv, page_table, table_width, seq_of_token, positions, write_kv));
     return check_launch("qk_norm_rope_append");
 }
 

@@ -46,6 +46,8 @@ struct GemmParams {
     int pair_offset;               // row offset of the second half of the pair
     int transposed;                // 0: out[m * ldo + n], 1: out[n * ldo + m]
     int out_f32;
+    int a_static;                  // A is never written by a kernel (weights): it may be fetched before the
+    int b_static;                  //   preceding kernel has finished; likewise B
     long long ldo;
     long long split_stride;        // elements between the partial results of two splits
     void* out;
@@ -137,22 +139,44 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
+    pdl_trigger();
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            for (int i = 0; i < n_kb; ++i) {
-                const int s = i % p.stages;
-                const uint32_t round = i / p.stages;
-                if (!mbar_wait(&empty_bar[s], (round & 1) ^ 1, &abort_flag, p.status, 1)) break;
+            auto load_a = [&](int i, int s) {
                 uint8_t* st = tiles + (size_t)s * stage_bytes;
-                mbar_expect_tx(&full_bar[s], stage_bytes);
                 const int kx = (kb_begin + i) * BK;
                 tma_load_2d(&map_a, &full_bar[s], st, kx, m0);
                 if (a_tiles == 2) tma_load_2d(&map_a, &full_bar[s], st + a_bytes, kx, m0 + p.pair_offset);
-                uint8_t* sb = st + a_tiles * a_bytes;
+            };
+            auto load_b = [&](int i, int s) {
+                uint8_t* sb = tiles + (size_t)s * stage_bytes + a_tiles * a_bytes;
+                const int kx = (kb_begin + i) * BK;
                 tma_load_2d(&map_b, &full_bar[s], sb, kx, n0);
                 if (b_tiles == 2) tma_load_2d(&map_b, &full_bar[s], sb + b_bytes, kx, n0 + p.pair_offset);
+            };
+            // The first ring of stages is free.  An operand that no kernel writes
+            // (weights) is fetched before the preceding kernel has finished; the
+            // other one only after pdl_wait.
+            const int first = min(n_kb, p.stages);
+            for (int i = 0; i < first; ++i) {
+                mbar_expect_tx(&full_bar[i], stage_bytes);
+                if (p.a_static) load_a(i, i);
+                if (p.b_static) load_b(i, i);
+            }
+            pdl_wait();
+            for (int i = 0; i < first; ++i) {
+                if (!p.a_static) load_a(i, i);
+                if (!p.b_static) load_b(i, i);
+            }
+            for (int i = first; i < n_kb; ++i) {
+                const int s = i % p.stages;
+                const uint32_t round = i / p.stages;
+                if (!mbar_wait(&empty_bar[s], (round & 1) ^ 1, &abort_flag, p.status, 1)) break;
+                mbar_expect_tx(&full_bar[s], stage_bytes);
+                load_a(i, s);
+                load_b(i, s);
             }
         }
     } else if (warp == 1) {
@@ -184,6 +208,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else {
         // ---------------- epilogue: tensor memory -> global ----------------
         const int q = warp & 3;                    // this warp reads lanes 32q .. 32q+31
+        pdl_wait();                                // the output may alias memory an earlier kernel still reads
         const bool ok = mbar_wait(&acc_bar, 0, &abort_flag, p.status, 3);
         tc_fence_after();
         const int m = m0 + q * 32 + lane;
@@ -299,10 +324,12 @@ using namespace wick;
 // the other half starts pair_offset rows further).
 // gated: 0 none, 1 pair in a, 2 pair in b.  transposed: out[n * ldo + m].
 // splits > 1 needs out_f32; partial s lies split_stride elements after s - 1.
+// a_static / b_static: that operand is never written by any kernel (weights), so
+// the kernel may fetch it before the kernel launched before it has finished.
 // status: device int that receives a non-zero code if a wait inside the kernel gave up.
 WICK_API int wick_gemm_tc(const void* a, long long a_total_rows, int a_rows, const void* b, long long b_total_rows,
                           int b_rows, int k, int bn, int gated, int pair_offset, int transposed, int out_f32,
-                          void* out, long long ldo, int splits, long long split_stride, int max_smem_bytes, int* status,
+                          int a_static, int b_static, void* out, long long ldo, int splits, long long split_stride, int max_smem_bytes, int* status,
                           void* stream) {
     WICK_REQUIRE(bn % 16 == 0 && bn >= 16 && bn <= 256, "gemm_tc: tile width %d must be a multiple of 16 in [16, 256]", bn);
     WICK_REQUIRE(!(gated == 2 && bn > 128) , "gemm_tc: a gated pair needs two accumulators: tile width <= 128");
@@ -334,8 +361,9 @@ WICK_API int wick_gemm_tc(const void* a, long long a_total_rows, int a_rows, con
     p.a_rows = a_rows; p.b_rows = b_rows; p.bn = bn; p.k_blocks = k_blocks; p.k_blocks_per_split = per_split;
     p.stages = stages; p.gated = gated; p.pair_offset = pair_offset; p.transposed = transposed; p.out_f32 = out_f32;
     p.ldo = ldo; p.split_stride = split_stride; p.out = out; p.status = status;
+    p.a_static = a_static; p.b_static = b_static;
     dim3 grid(ceil_div(a_rows, BM), ceil_div(b_rows, bn), splits);
     WICK_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "gemm_tc: grid limit");
-    gemm_tc_kernel<<<grid, NUM_THREADS, smem, (cudaStream_t)stream>>>(map_a, map_b, p);
+    WICK_CUDA(launch(gemm_tc_kernel, grid, dim3(NUM_THREADS), (size_t)smem, (cudaStream_t)stream, map_a, map_b, p));
     return check_launch("gemm_tc");
 }

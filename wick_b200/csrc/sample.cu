@@ -16,6 +16,8 @@ constexpr int ST = 1024;
 __global__ void __launch_bounds__(ST) argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab) {
     __shared__ float sv[32];
     __shared__ int si[32];
+    pdl_trigger();
+    pdl_wait();
     const float* x = logits + (int64_t)blockIdx.x * vocab;
     float best = -INFINITY;
     int idx = INT_MAX;
@@ -221,7 +223,7 @@ using namespace wick;
 WICK_API int wick_argmax(const float* logits, int* out, int rows, int vocab, void* s) {
     WICK_REQUIRE(vocab > 0 && rows >= 0, "argmax: bad sizes");
     if (rows == 0) return 0;
-    argmax_kernel<<<rows, ST, 0, (cudaStream_t)s>>>(logits, out, vocab);
+    WICK_CUDA(launch(argmax_kernel, dim3(rows), dim3(ST), 0, (cudaStream_t)s, logits, out, vocab));
     return check_launch("argmax");
 }
 

@@ -33,12 +33,12 @@ def _lib() -> _Lib:
     return lib
 
 
-_SIG = "plipliiiiiiiplilipp"
+_SIG = "plipliiiiiiiiiplilipp"
 
 
 def gemm_tc(a: torch.Tensor, a_rows: int, b: torch.Tensor, b_rows: int, *, bn: int, out: torch.Tensor, ldo: int,
             gated: int = 0, pair_offset: int = 0, transposed: bool = False, splits: int = 1, split_stride: int = 0,
-            max_smem: int = 0) -> None:
+            max_smem: int = 0, a_static: bool = False, b_static: bool = False) -> None:
     """The raw kernel call (see ``wick_gemm_tc`` in gemm_tc.cu)."""
     for nm, t in (("a", a), ("b", b)):
         if not (t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous() and t.dim() == 2):
@@ -49,7 +49,8 @@ def gemm_tc(a: torch.Tensor, a_rows: int, b: torch.Tensor, b_rows: int, *, bn: i
         raise KernelError("gemm_tc: out must be contiguous float32 or bfloat16")
     st = status_tensor(a.device)
     _lib().call("wick_gemm_tc", _SIG, _p(a), a.shape[0], a_rows, _p(b), b.shape[0], b_rows, a.shape[1], bn, gated,
-                pair_offset, 1 if transposed else 0, 1 if out.dtype == torch.float32 else 0, _p(out), ldo, splits,
+                pair_offset, 1 if transposed else 0, 1 if out.dtype == torch.float32 else 0, 1 if a_static else 0,
+                1 if b_static else 0, _p(out), ldo, splits,
                 split_stride, max_smem, _p(st), _stream())
 
 
@@ -95,12 +96,13 @@ class Plan:
             blocks = (self.n_out + 127) // 128 * splits
             gemm_tc(self.w, self.n_out, x, t, bn=_ceil16(t), out=out, ldo=self.n_out,
                     gated=1 if self.gated else 0, pair_offset=self.n_out, transposed=True, splits=splits,
-                    split_stride=t * self.n_out, max_smem=(200 if blocks <= N_SMS else 100) * 1024)
+                    split_stride=t * self.n_out, max_smem=(200 if blocks <= N_SMS else 100) * 1024,
+                    a_static=True)
         else:
             bn = min(128 if self.gated else 256, _ceil16(self.n_out))
             gemm_tc(x, t, self.w, self.n_out, bn=bn, out=out, ldo=self.n_out, gated=2 if self.gated else 0,
                     pair_offset=self.n_out, transposed=False, splits=splits, split_stride=t * self.n_out,
-                    max_smem=200 * 1024)
+                    max_smem=200 * 1024, b_static=True)
 
 
 def plan_for(weight: torch.Tensor, gated: bool = False) -> Optional[Plan]:
