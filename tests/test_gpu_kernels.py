@@ -306,7 +306,7 @@ def _tc_ref(x, w, gated):
 @pytest.mark.parametrize("t, n, k, gated", [
     (1, 128, 64, False), (5, 333, 72, False), (8, 256, 128, False), (64, 1000, 96, False), (3, 200, 104, True),
     (16, 384, 1024, False), (65, 333, 72, False), (128, 16, 64, False), (300, 520, 200, False), (300, 520, 200, True),
-    (1000, 1024, 512, True), (33, 4096, 4096, False)])
+    (1000, 1024, 512, True), (33, 4096, 4096, False), (8, 1000, 256, True), (40, 333, 2048, True)])
 def test_gemm_tensor_core_both_ways_round(t, n, k, gated):
     """Few tokens (weights as the 128-row operand, transposed output, split inner
     dimension) and many tokens (tokens as the 128-row operand), plain and gated,

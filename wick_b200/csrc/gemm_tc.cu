@@ -42,7 +42,8 @@ struct GemmParams {
     int k_blocks;                  // ceil(k / 64)
     int k_blocks_per_split;
     int stages;
-    int gated;                     // 0 none, 1 the pair lives in A, 2 the pair lives in B
+    int gated;                     // 0 none, 1 the pair lives in A (two tiles), 2 the pair lives in B (two tiles),
+                                   // 3 the pair lives in A and shares one tile: rows 0-63 gate, rows 64-127 up
     int pair_offset;               // row offset of the second half of the pair
     int transposed;                // 0: out[m * ldo + n], 1: out[n * ldo + m]
     int out_f32;
@@ -106,9 +107,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __shared__ uint64_t acc_bar;
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
+    __shared__ float xch[2][64][17];           // gated == 3: up values on their way to the warps that hold the gate values
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * BM;
+    const int m0 = blockIdx.x * (p.gated == 3 ? BM / 2 : BM);
     const int n0 = blockIdx.y * p.bn;
     const int kb_begin = blockIdx.z * p.k_blocks_per_split;
     const int kb_end = min(p.k_blocks, kb_begin + p.k_blocks_per_split);
@@ -118,7 +120,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t a_bytes = BM * BK * 2, b_bytes = (uint32_t)p.bn * BK * 2;
     const uint32_t stage_bytes = a_tiles * a_bytes + b_tiles * b_bytes;
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    const int n_acc = p.gated ? 2 : 1;
+    const int n_acc = (p.gated == 1 || p.gated == 2) ? 2 : 1;
     uint32_t tmem_cols = 32;
     while (tmem_cols < (uint32_t)(n_acc * p.bn)) tmem_cols <<= 1;
 
@@ -149,6 +151,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const int kx = (kb_begin + i) * BK;
                 tma_load_2d(&map_a, &full_bar[s], st, kx, m0);
                 if (a_tiles == 2) tma_load_2d(&map_a, &full_bar[s], st + a_bytes, kx, m0 + p.pair_offset);
+                if (p.gated == 3) tma_load_2d(&map_a, &full_bar[s], st + a_bytes / 2, kx, m0 + p.pair_offset);   // 64-row boxes
             };
             auto load_b = [&](int i, int s) {
                 uint8_t* sb = tiles + (size_t)s * stage_bytes + a_tiles * a_bytes;
@@ -209,12 +212,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // ---------------- epilogue: tensor memory -> global ----------------
         const int q = warp & 3;                    // this warp reads lanes 32q .. 32q+31
         pdl_wait();                                // the output may alias memory an earlier kernel still reads
-        const bool ok = mbar_wait(&acc_bar, 0, &abort_flag, p.status, 3);
+        const bool ok = __all_sync(0xffffffffu, mbar_wait(&acc_bar, 0, &abort_flag, p.status, 3));   // one answer per warp
         tc_fence_after();
         const int m = m0 + q * 32 + lane;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
         char* out_base = (char*)p.out + (size_t)blockIdx.z * p.split_stride * (p.out_f32 ? 4 : 2);
-        if (ok && n_kb > 0) {
+        if (p.gated == 3) {
+            // Lanes 0-63 of the accumulator hold gate rows, lanes 64-127 the up rows of
+            // the same outputs.  Warps 2 and 3 pass their values through shared memory
+            // to warps 0 and 1, which finish and store (transposed output only).
+            const int mg = m0 + (q & 1) * 32 + lane;
+            for (int c0 = 0; c0 < p.bn; c0 += 16) {
+                float v[16];
+                if (ok && n_kb > 0) tc_ld16(lane_addr + c0, v);
+                float (*buf)[17] = xch[(c0 >> 4) & 1];
+                if (q >= 2) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) buf[(q - 2) * 32 + lane][j] = v[j];
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (q < 2 && ok && n_kb > 0 && mg < p.a_rows) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int n = n0 + c0 + j;
+                        if (n < p.b_rows) {
+                            const float g = v[j], u = buf[q * 32 + lane][j];
+                            const float r = g / (1.0f + expf(-g)) * u;
+                            const long long off = (long long)n * p.ldo + mg;
+                            if (p.out_f32) ((float*)out_base)[off] = r;
+                            else ((__nv_bfloat16*)out_base)[off] = __float2bfloat16_rn(r);
+                        }
+                    }
+                }
+            }
+        } else if (ok && n_kb > 0) {
             for (int c0 = 0; c0 < p.bn; c0 += 16) {
                 float v[16];
                 tc_ld16(lane_addr + c0, v);
@@ -333,7 +364,8 @@ WICK_API int wick_gemm_tc(const void* a, long long a_total_rows, int a_rows, con
                           void* stream) {
     WICK_REQUIRE(bn % 16 == 0 && bn >= 16 && bn <= 256, "gemm_tc: tile width %d must be a multiple of 16 in [16, 256]", bn);
     WICK_REQUIRE(!(gated == 2 && bn > 128) , "gemm_tc: a gated pair needs two accumulators: tile width <= 128");
-    WICK_REQUIRE(gated >= 0 && gated <= 2 && splits >= 1, "gemm_tc: bad options");
+    WICK_REQUIRE(gated >= 0 && gated <= 3 && splits >= 1, "gemm_tc: bad options");
+    WICK_REQUIRE(gated != 3 || transposed, "gemm_tc: the shared-tile pair is built for the transposed output only");
     WICK_REQUIRE(splits == 1 || (out_f32 && !gated), "gemm_tc: a split inner dimension needs plain float32 partial sums");
     WICK_REQUIRE(a_rows > 0 && b_rows >= 0 && k > 0, "gemm_tc: bad sizes");
     if (b_rows == 0) return 0;
@@ -342,11 +374,11 @@ WICK_API int wick_gemm_tc(const void* a, long long a_total_rows, int a_rows, con
     const int per_split = ceil_div(k_blocks, splits);
     WICK_REQUIRE((long long)(splits - 1) * per_split < k_blocks, "gemm_tc: a split would be empty");
     CUtensorMap map_a, map_b;
-    if (int e = make_map(&map_a, a, a_total_rows, k, BM)) return e;
+    if (int e = make_map(&map_a, a, a_total_rows, k, gated == 3 ? BM / 2 : BM)) return e;
     if (int e = make_map(&map_b, b, b_total_rows, k, bn)) return e;
     const int stage_bytes = (gated == 1 ? 2 : 1) * BM * BK * 2 + (gated == 2 ? 2 : 1) * bn * BK * 2;
     int budget = max_smem_bytes > 0 ? max_smem_bytes : 200 * 1024;
-    if (budget > 220 * 1024) budget = 220 * 1024;
+    if (budget > 208 * 1024) budget = 208 * 1024;     // 227 KB per block minus the static arrays
     int stages = (budget - 1024) / stage_bytes;
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     if (stages > per_split) stages = per_split < 2 ? 2 : per_split;
@@ -354,15 +386,15 @@ WICK_API int wick_gemm_tc(const void* a, long long a_total_rows, int a_rows, con
     const int smem = stages * stage_bytes + 1024;
     static int raised = 0;
     if (smem > raised) {
-        WICK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 221 * 1024));
-        raised = 221 * 1024;
+        WICK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024));
+        raised = 210 * 1024;
     }
     GemmParams p;
     p.a_rows = a_rows; p.b_rows = b_rows; p.bn = bn; p.k_blocks = k_blocks; p.k_blocks_per_split = per_split;
     p.stages = stages; p.gated = gated; p.pair_offset = pair_offset; p.transposed = transposed; p.out_f32 = out_f32;
     p.ldo = ldo; p.split_stride = split_stride; p.out = out; p.status = status;
     p.a_static = a_static; p.b_static = b_static;
-    dim3 grid(ceil_div(a_rows, BM), ceil_div(b_rows, bn), splits);
+    dim3 grid(ceil_div(a_rows, gated == 3 ? BM / 2 : BM), ceil_div(b_rows, bn), splits);
     WICK_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "gemm_tc: grid limit");
     WICK_CUDA(launch(gemm_tc_kernel, grid, dim3(NUM_THREADS), (size_t)smem, (cudaStream_t)stream, map_a, map_b, p));
     return check_launch("gemm_tc");

@@ -66,7 +66,9 @@ class Plan:
         self.n_out = self.rows // 2 if gated else self.rows
         k_blocks = (self.k + 63) // 64
         tiles = (self.n_out + 127) // 128
-        self.decode_splits = max(1, min(N_SMS // tiles, 8, k_blocks // 8))
+        # Decode: about two blocks per SM (just under 2 x 148) stream best; every
+        # split keeps at least eight 64-wide steps of the inner dimension.
+        self.decode_splits = max(1, min(2 * N_SMS // tiles, 8, k_blocks // 8))
 
     # ---- [n, in] -> [n, out] ----
     def forward(self, x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
@@ -90,14 +92,12 @@ class Plan:
     def _run(self, x: torch.Tensor, out: torch.Tensor, splits: int) -> None:
         t = x.shape[0]
         if t <= SMALL:
-            # One block per SM with a deep ring when the blocks fit in one wave; two
-            # smaller ones per SM when there are several waves, so that one block's
-            # start and end overlap another's streaming.
-            blocks = (self.n_out + 127) // 128 * splits
+            # Two blocks of 100 KB per SM: one block's start and end overlap the
+            # other's streaming.  A gated pair shares one 128-row tile (64 gate rows,
+            # 64 up rows), which doubles the number of blocks.
             gemm_tc(self.w, self.n_out, x, t, bn=_ceil16(t), out=out, ldo=self.n_out,
-                    gated=1 if self.gated else 0, pair_offset=self.n_out, transposed=True, splits=splits,
-                    split_stride=t * self.n_out, max_smem=(200 if blocks <= N_SMS else 100) * 1024,
-                    a_static=True)
+                    gated=3 if self.gated else 0, pair_offset=self.n_out, transposed=True, splits=splits,
+                    split_stride=t * self.n_out, max_smem=100 * 1024, a_static=True)
         else:
             bn = min(128 if self.gated else 256, _ceil16(self.n_out))
             gemm_tc(x, t, self.w, self.n_out, bn=bn, out=out, ldo=self.n_out, gated=2 if self.gated else 0,
