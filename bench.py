@@ -151,6 +151,7 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="no batch 1 / 64 runs")
     ap.add_argument("--skip-e2e", action="store_true", help="no run through the Python entry point")
     ap.add_argument("--skip-prefill", action="store_true")
+    ap.add_argument("--skip-decode", action="store_true", help="prefill only (for profiling)")
     ap.add_argument("--eager", action="store_true", help="no CUDA graphs (every kernel is a launch of its own)")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -186,7 +187,10 @@ def main() -> int:
 
     # ---- decode, device-timed (the headline value) ----
     with Clocks() as clk:
-        ms, launches, kv_tokens = device_timed_decode(torch, wick, ops, eng, args.batch, steps, warmup, vocab, 1)
+        if args.skip_decode:
+            ms, launches, kv_tokens = float("nan"), 0, 0
+        else:
+            ms, launches, kv_tokens = device_timed_decode(torch, wick, ops, eng, args.batch, steps, warmup, vocab, 1)
     value = args.batch * 1e3 / ms
     step_bytes = weight_bytes + kv_tokens * kv_bytes_per_token
     achieved = step_bytes / (ms * 1e-3) / 1e9
@@ -197,7 +201,7 @@ def main() -> int:
     prompts = [torch.randint(0, vocab, (PROMPT,), generator=g).tolist() for _ in range(args.batch)]
     opts = wick.GenOptions(max_tokens=steps + 1, sampler=wick.SamplerConfig.greedy(), context=CONTEXT,
                            max_batch=args.batch)
-    if not args.skip_e2e:
+    if not args.skip_e2e and not args.skip_decode:
         wick.generate(eng, [p[:16] for p in prompts], wick.GenOptions(max_tokens=4, sampler=wick.SamplerConfig.greedy(),
                                                                       context=CONTEXT, max_batch=args.batch))
         res = wick.generate(eng, prompts, opts)
@@ -233,7 +237,7 @@ def main() -> int:
 
     # ---- other batch sizes ----
     points = {}
-    if not args.skip_points:
+    if not args.skip_points and not args.skip_decode:
         for b in (1, 64):
             pms_b, _, _ = device_timed_decode(torch, wick, ops, eng, b, min(steps, 64), warmup, vocab, 10 + b)
             points[f"decode_b{b}"] = b * 1e3 / pms_b
