@@ -47,6 +47,7 @@ struct GemmParams {
     int pair_offset;               // row offset of the second half of the pair
     int transposed;                // 0: out[m * ldo + n], 1: out[n * ldo + m]
     int out_f32;
+    int total_tiles, grid_m, grid_n;   // tiles = grid_m * grid_n * splits, the m tile varying fastest
     int a_static;                  // A is never written by a kernel (weights): it may be fetched before the
     int b_static;                  //   preceding kernel has finished; likewise B
     long long ldo;
@@ -99,30 +100,59 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
     return d;
 }
 
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// Persistent: block b works on tiles b, b + gridDim.x, ...  A tile is (m tile, n
+// tile, split) with the m tile varying fastest, so that blocks running at the
+// same time share B tiles through the L2 cache.  With two accumulators in tensor
+// memory the epilogue of one tile overlaps the main loop of the next.
+template <bool PERSIST, int GATED, bool TRANSPOSED, bool OUT_F32>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t full_bar[MAX_STAGES];
     __shared__ uint64_t empty_bar[MAX_STAGES];
-    __shared__ uint64_t acc_bar;
+    __shared__ uint64_t acc_full[2];
+    __shared__ uint64_t acc_empty[2];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
+    __shared__ int ok_w[4];
     __shared__ float xch[2][64][17];           // gated == 3: up values on their way to the warps that hold the gate values
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * (p.gated == 3 ? BM / 2 : BM);
-    const int n0 = blockIdx.y * p.bn;
-    const int kb_begin = blockIdx.z * p.k_blocks_per_split;
-    const int kb_end = min(p.k_blocks, kb_begin + p.k_blocks_per_split);
-    const int n_kb = kb_end - kb_begin;
-
-    const int a_tiles = p.gated == 1 ? 2 : 1, b_tiles = p.gated == 2 ? 2 : 1;
+    const int tile_m = GATED == 3 ? BM / 2 : BM;
+    const int a_tiles = GATED == 1 ? 2 : 1, b_tiles = GATED == 2 ? 2 : 1;
     const uint32_t a_bytes = BM * BK * 2, b_bytes = (uint32_t)p.bn * BK * 2;
     const uint32_t stage_bytes = a_tiles * a_bytes + b_tiles * b_bytes;
     uint8_t* tiles = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    const int n_acc = (p.gated == 1 || p.gated == 2) ? 2 : 1;
+    const int n_acc = (GATED == 1 || GATED == 2) ? 2 : 1;
+    const int acc_cols = n_acc * p.bn;                       // columns of one tile's accumulators
+    // PERSIST: block b runs tiles b, b + gridDim.x, ...; otherwise the grid is (m tiles, n tiles, splits).
+    const int my_tiles = PERSIST ? (p.total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 1;
+    const int w_first = PERSIST ? (int)blockIdx.x : 0, w_end = PERSIST ? p.total_tiles : 1;
+    const int w_step = PERSIST ? (int)gridDim.x : 1;
+    const int acc_bufs = (my_tiles > 1 && 2 * acc_cols <= 512) ? 2 : 1;
     uint32_t tmem_cols = 32;
-    while (tmem_cols < (uint32_t)(n_acc * p.bn)) tmem_cols <<= 1;
+    while (tmem_cols < (uint32_t)(acc_bufs * acc_cols)) tmem_cols <<= 1;
+
+    auto tile_coords = [&](int w, int& m0, int& n0, int& kb_begin, int& n_kb, int& z) {
+        int x, y;
+        if (PERSIST) {
+            x = w % p.grid_m;
+            y = (w / p.grid_m) % p.grid_n;
+            z = w / (p.grid_m * p.grid_n);
+        } else {                                             // one tile per block: a three-dimensional grid
+            x = blockIdx.x;
+            y = blockIdx.y;
+            z = blockIdx.z;
+        }
+        m0 = x * tile_m;
+        n0 = y * p.bn;
+        kb_begin = z * p.k_blocks_per_split;
+        n_kb = min(p.k_blocks, kb_begin + p.k_blocks_per_split) - kb_begin;
+    };
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -130,7 +160,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             mbar_init(&full_bar[s], 1);
             mbar_init(&empty_bar[s], 1);
         }
-        mbar_init(&acc_bar, 1);
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&acc_full[i], 1);
+            mbar_init(&acc_empty[i], 4);                     // one arrival per epilogue warp
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -146,40 +179,51 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            auto load_a = [&](int i, int s) {
-                uint8_t* st = tiles + (size_t)s * stage_bytes;
-                const int kx = (kb_begin + i) * BK;
-                tma_load_2d(&map_a, &full_bar[s], st, kx, m0);
-                if (a_tiles == 2) tma_load_2d(&map_a, &full_bar[s], st + a_bytes, kx, m0 + p.pair_offset);
-                if (p.gated == 3) tma_load_2d(&map_a, &full_bar[s], st + a_bytes / 2, kx, m0 + p.pair_offset);   // 64-row boxes
-            };
-            auto load_b = [&](int i, int s) {
-                uint8_t* sb = tiles + (size_t)s * stage_bytes + a_tiles * a_bytes;
-                const int kx = (kb_begin + i) * BK;
-                tma_load_2d(&map_b, &full_bar[s], sb, kx, n0);
-                if (b_tiles == 2) tma_load_2d(&map_b, &full_bar[s], sb + b_bytes, kx, n0 + p.pair_offset);
-            };
-            // The first ring of stages is free.  An operand that no kernel writes
-            // (weights) is fetched before the preceding kernel has finished; the
-            // other one only after pdl_wait.
-            const int first = min(n_kb, p.stages);
-            for (int i = 0; i < first; ++i) {
-                mbar_expect_tx(&full_bar[i], stage_bytes);
-                if (p.a_static) load_a(i, i);
-                if (p.b_static) load_b(i, i);
-            }
-            pdl_wait();
-            for (int i = 0; i < first; ++i) {
-                if (!p.a_static) load_a(i, i);
-                if (!p.b_static) load_b(i, i);
-            }
-            for (int i = first; i < n_kb; ++i) {
-                const int s = i % p.stages;
-                const uint32_t round = i / p.stages;
-                if (!mbar_wait(&empty_bar[s], (round & 1) ^ 1, &abort_flag, p.status, 1)) break;
-                mbar_expect_tx(&full_bar[s], stage_bytes);
-                load_a(i, s);
-                load_b(i, s);
+            uint32_t it = 0;                                 // 64-wide steps issued so far, over all tiles
+            bool ok = true;
+            for (int w = w_first; w < w_end && ok; w += w_step) {
+                int m0, n0, kb_begin, n_kb, z;
+                tile_coords(w, m0, n0, kb_begin, n_kb, z);
+                auto load_a = [&](int i, int s) {
+                    uint8_t* st = tiles + (size_t)s * stage_bytes;
+                    const int kx = (kb_begin + i) * BK;
+                    tma_load_2d(&map_a, &full_bar[s], st, kx, m0);
+                    if (a_tiles == 2) tma_load_2d(&map_a, &full_bar[s], st + a_bytes, kx, m0 + p.pair_offset);
+                    if (GATED == 3) tma_load_2d(&map_a, &full_bar[s], st + a_bytes / 2, kx, m0 + p.pair_offset);   // 64-row boxes
+                };
+                auto load_b = [&](int i, int s) {
+                    uint8_t* sb = tiles + (size_t)s * stage_bytes + a_tiles * a_bytes;
+                    const int kx = (kb_begin + i) * BK;
+                    tma_load_2d(&map_b, &full_bar[s], sb, kx, n0);
+                    if (b_tiles == 2) tma_load_2d(&map_b, &full_bar[s], sb + b_bytes, kx, n0 + p.pair_offset);
+                };
+                int i = 0;
+                if (it == 0) {
+                    // The first ring of stages is free.  An operand that no kernel
+                    // writes (weights) is fetched before the preceding kernel has
+                    // finished; the other one only after pdl_wait.
+                    const int first = min(n_kb, p.stages);
+                    for (int j = 0; j < first; ++j) {
+                        mbar_expect_tx(&full_bar[j], stage_bytes);
+                        if (p.a_static) load_a(j, j);
+                        if (p.b_static) load_b(j, j);
+                    }
+                    pdl_wait();
+                    for (int j = 0; j < first; ++j) {
+                        if (!p.a_static) load_a(j, j);
+                        if (!p.b_static) load_b(j, j);
+                    }
+                    i = first;
+                    it = first;
+                }
+                for (; i < n_kb; ++i, ++it) {
+                    const int s = it % p.stages;
+                    const uint32_t round = it / p.stages;
+                    if (!mbar_wait(&empty_bar[s], (round & 1) ^ 1, &abort_flag, p.status, 1)) { ok = false; break; }
+                    mbar_expect_tx(&full_bar[s], stage_bytes);
+                    load_a(i, s);
+                    load_b(i, s);
+                }
             }
         }
     } else if (warp == 1) {
@@ -187,112 +231,147 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (lane == 0) {
             // kind::f16, A and B bfloat16 and k-major, float32 accumulator, M = 128, N = bn
             const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(p.bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            uint32_t it = 0;
             bool ok = true;
-            for (int i = 0; i < n_kb && ok; ++i) {
-                const int s = i % p.stages;
-                const uint32_t round = i / p.stages;
-                ok = mbar_wait(&full_bar[s], round & 1, &abort_flag, p.status, 2);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t sa = smem_u32(tiles + (size_t)s * stage_bytes);
-                const uint32_t sb = sa + a_tiles * a_bytes;
-#pragma unroll
-                for (int k = 0; k < BK / UMMA_K; ++k) {
-                    const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
-                    const uint64_t da = smem_desc(sa + k * UMMA_K * 2), db = smem_desc(sb + k * UMMA_K * 2);
-                    tc_mma(tmem_base, da, db, idesc, acc);
-                    if (p.gated == 1) tc_mma(tmem_base + p.bn, smem_desc(sa + a_bytes + k * UMMA_K * 2), db, idesc, acc);
-                    if (p.gated == 2) tc_mma(tmem_base + p.bn, da, smem_desc(sb + b_bytes + k * UMMA_K * 2), idesc, acc);
+            int t = 0;
+            for (int w = w_first; w < w_end && ok; w += w_step, ++t) {
+                int m0, n0, kb_begin, n_kb, z;
+                tile_coords(w, m0, n0, kb_begin, n_kb, z);
+                const int buf = acc_bufs == 2 ? (t & 1) : 0;
+                const uint32_t use = acc_bufs == 2 ? (uint32_t)(t >> 1) : (uint32_t)t;   // how often this buffer was used before
+                if (t > 0) {
+                    ok = mbar_wait(&acc_empty[buf], (use & 1) ^ 1, &abort_flag, p.status, 5);  // the epilogue has drained it
+                    if (!ok) break;
+                    tc_fence_after();
                 }
-                tc_commit(&empty_bar[s]);          // the stage is free once these instructions have read it
+                const uint32_t d0 = tmem_base + buf * acc_cols;
+                for (int i = 0; i < n_kb; ++i, ++it) {
+                    const int s = it % p.stages;
+                    const uint32_t round = it / p.stages;
+                    ok = mbar_wait(&full_bar[s], round & 1, &abort_flag, p.status, 2);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(tiles + (size_t)s * stage_bytes);
+                    const uint32_t sb = sa + a_tiles * a_bytes;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+                        const uint64_t da = smem_desc(sa + k * UMMA_K * 2), db = smem_desc(sb + k * UMMA_K * 2);
+                        tc_mma(d0, da, db, idesc, acc);
+                        if (GATED == 1) tc_mma(d0 + p.bn, smem_desc(sa + a_bytes + k * UMMA_K * 2), db, idesc, acc);
+                        if (GATED == 2) tc_mma(d0 + p.bn, da, smem_desc(sb + b_bytes + k * UMMA_K * 2), idesc, acc);
+                    }
+                    tc_commit(&empty_bar[s]);      // the stage is free once these instructions have read it
+                }
+                tc_commit(&acc_full[buf]);         // this tile's accumulator is complete
             }
-            tc_commit(&acc_bar);                   // the accumulator is complete
         }
     } else {
         // ---------------- epilogue: tensor memory -> global ----------------
         const int q = warp & 3;                    // this warp reads lanes 32q .. 32q+31
         pdl_wait();                                // the output may alias memory an earlier kernel still reads
-        const bool ok = __all_sync(0xffffffffu, mbar_wait(&acc_bar, 0, &abort_flag, p.status, 3));   // one answer per warp
-        tc_fence_after();
-        const int m = m0 + q * 32 + lane;
-        const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
-        char* out_base = (char*)p.out + (size_t)blockIdx.z * p.split_stride * (p.out_f32 ? 4 : 2);
-        if (p.gated == 3) {
-            // Lanes 0-63 of the accumulator hold gate rows, lanes 64-127 the up rows of
-            // the same outputs.  Warps 2 and 3 pass their values through shared memory
-            // to warps 0 and 1, which finish and store (transposed output only).
-            const int mg = m0 + (q & 1) * 32 + lane;
-            for (int c0 = 0; c0 < p.bn; c0 += 16) {
-                float v[16];
-                if (ok && n_kb > 0) tc_ld16(lane_addr + c0, v);
-                float (*buf)[17] = xch[(c0 >> 4) & 1];
-                if (q >= 2) {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) buf[(q - 2) * 32 + lane][j] = v[j];
-                }
+        int t = 0;
+        for (int w = w_first; w < w_end; w += w_step, ++t) {
+            int m0, n0, kb_begin, n_kb, z;
+            tile_coords(w, m0, n0, kb_begin, n_kb, z);
+            const int buf = acc_bufs == 2 ? (t & 1) : 0;
+            const uint32_t use = acc_bufs == 2 ? (uint32_t)(t >> 1) : (uint32_t)t;
+            const int m = m0 + q * 32 + lane;
+            const uint32_t lane_addr = tmem_base + buf * acc_cols + ((uint32_t)(q * 32) << 16);
+            char* out_base = (char*)p.out + (size_t)z * p.split_stride * (OUT_F32 ? 4 : 2);
+            // One answer for the four epilogue warps, so that they leave the loop together.
+            const bool ok_warp = __all_sync(0xffffffffu, mbar_wait(&acc_full[buf], use & 1, &abort_flag, p.status, 3));
+            bool ok = ok_warp;
+            if (my_tiles > 1 || GATED == 3) {            // (a block with one plain tile has nothing left to agree on)
+                if (lane == 0) ok_w[q] = ok_warp ? 1 : 0;
                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (q < 2 && ok && n_kb > 0 && mg < p.a_rows) {
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int n = n0 + c0 + j;
-                        if (n < p.b_rows) {
-                            const float g = v[j], u = buf[q * 32 + lane][j];
-                            const float r = g / (1.0f + expf(-g)) * u;
-                            const long long off = (long long)n * p.ldo + mg;
-                            if (p.out_f32) ((float*)out_base)[off] = r;
-                            else ((__nv_bfloat16*)out_base)[off] = __float2bfloat16_rn(r);
-                        }
-                    }
-                }
+                ok = ok_w[0] && ok_w[1] && ok_w[2] && ok_w[3];
+                asm volatile("bar.sync 1, 128;" ::: "memory");
             }
-        } else if (ok && n_kb > 0) {
-            for (int c0 = 0; c0 < p.bn; c0 += 16) {
-                float v[16];
-                tc_ld16(lane_addr + c0, v);
-                if (p.gated) {
-                    float u[16];
-                    tc_ld16(lane_addr + p.bn + c0, u);
+            tc_fence_after();
+            if (GATED == 3) {
+                // Lanes 0-63 of the accumulator hold gate rows, lanes 64-127 the up rows of
+                // the same outputs.  Warps 2 and 3 pass their values through shared memory
+                // to warps 0 and 1, which finish and store (transposed output only).
+                const int mg = m0 + (q & 1) * 32 + lane;
+                for (int c0 = 0; c0 < p.bn; c0 += 16) {
+                    float v[16];
+                    if (ok && n_kb > 0) tc_ld16(lane_addr + c0, v);
+                    float (*xb)[17] = xch[(c0 >> 4) & 1];
+                    if (q >= 2) {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) v[j] = v[j] / (1.0f + expf(-v[j])) * u[j];
-                }
-                if (m < p.a_rows) {
-                    if (!p.transposed) {
-                        const int n_left = p.b_rows - (n0 + c0);
-                        const long long off = (long long)m * p.ldo + n0 + c0;
-                        if (p.out_f32) {
-                            float* o = (float*)out_base + off;
-                            if (n_left >= 16 && (off & 3) == 0) {
-#pragma unroll
-                                for (int j = 0; j < 16; j += 4) *(float4*)(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                            } else {
-                                for (int j = 0; j < 16 && j < n_left; ++j) o[j] = v[j];
-                            }
-                        } else {
-                            __nv_bfloat16* o = (__nv_bfloat16*)out_base + off;
-                            if (n_left >= 16 && (off & 7) == 0) {
-                                uint4 w[2];
-                                __nv_bfloat162* h = (__nv_bfloat162*)w;
-#pragma unroll
-                                for (int j = 0; j < 8; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-                                *(uint4*)o = w[0];
-                                *(uint4*)(o + 8) = w[1];
-                            } else {
-                                for (int j = 0; j < 16 && j < n_left; ++j) o[j] = __float2bfloat16_rn(v[j]);
-                            }
-                        }
-                    } else {
+                        for (int j = 0; j < 16; ++j) xb[(q - 2) * 32 + lane][j] = v[j];
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (q < 2 && ok && n_kb > 0 && mg < p.a_rows) {
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
                             const int n = n0 + c0 + j;
                             if (n < p.b_rows) {
-                                const long long off = (long long)n * p.ldo + m;
-                                if (p.out_f32) ((float*)out_base)[off] = v[j];
-                                else ((__nv_bfloat16*)out_base)[off] = __float2bfloat16_rn(v[j]);
+                                const float g = v[j], u = xb[q * 32 + lane][j];
+                                const float r = g / (1.0f + expf(-g)) * u;
+                                const long long off = (long long)n * p.ldo + mg;
+                                if (OUT_F32) ((float*)out_base)[off] = r;
+                                else ((__nv_bfloat16*)out_base)[off] = __float2bfloat16_rn(r);
+                            }
+                        }
+                    }
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");     // the exchange buffers are free for the next tile
+            } else if (ok && n_kb > 0) {
+                for (int c0 = 0; c0 < p.bn; c0 += 16) {
+                    float v[16];
+                    tc_ld16(lane_addr + c0, v);
+                    if (GATED) {
+                        float u[16];
+                        tc_ld16(lane_addr + p.bn + c0, u);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) v[j] = v[j] / (1.0f + expf(-v[j])) * u[j];
+                    }
+                    if (m < p.a_rows) {
+                        if (!TRANSPOSED) {
+                            const int n_left = p.b_rows - (n0 + c0);
+                            const long long off = (long long)m * p.ldo + n0 + c0;
+                            if (OUT_F32) {
+                                float* o = (float*)out_base + off;
+                                if (n_left >= 16 && (off & 3) == 0) {
+#pragma unroll
+                                    for (int j = 0; j < 16; j += 4) *(float4*)(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                                } else {
+                                    for (int j = 0; j < 16 && j < n_left; ++j) o[j] = v[j];
+                                }
+                            } else {
+                                __nv_bfloat16* o = (__nv_bfloat16*)out_base + off;
+                                if (n_left >= 16 && (off & 7) == 0) {
+                                    uint4 wv[2];
+                                    __nv_bfloat162* h = (__nv_bfloat162*)wv;
+#pragma unroll
+                                    for (int j = 0; j < 8; ++j) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                                    *(uint4*)o = wv[0];
+                                    *(uint4*)(o + 8) = wv[1];
+                                } else {
+                                    for (int j = 0; j < 16 && j < n_left; ++j) o[j] = __float2bfloat16_rn(v[j]);
+                                }
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                const int n = n0 + c0 + j;
+                                if (n < p.b_rows) {
+                                    const long long off = (long long)n * p.ldo + m;
+                                    if (OUT_F32) ((float*)out_base)[off] = v[j];
+                                    else ((__nv_bfloat16*)out_base)[off] = __float2bfloat16_rn(v[j]);
+                                }
                             }
                         }
                     }
                 }
             }
+            // this warp has read what it needs of the accumulator: hand the buffer back
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+            if (!ok) break;
         }
     }
 
@@ -366,6 +445,8 @@ WICK_API int wick_gemm_tc(const void* a, long long a_total_rows, int a_rows, con
     WICK_REQUIRE(!(gated == 2 && bn > 128) , "gemm_tc: a gated pair needs two accumulators: tile width <= 128");
     WICK_REQUIRE(gated >= 0 && gated <= 3 && splits >= 1, "gemm_tc: bad options");
     WICK_REQUIRE(gated != 3 || transposed, "gemm_tc: the shared-tile pair is built for the transposed output only");
+    WICK_REQUIRE(gated != 1 || transposed, "gemm_tc: a pair in the 128-row operand goes with the transposed output");
+    WICK_REQUIRE(gated != 2 || !transposed, "gemm_tc: a pair in the narrow operand goes with the row-major output");
     WICK_REQUIRE(splits == 1 || (out_f32 && !gated), "gemm_tc: a split inner dimension needs plain float32 partial sums");
     WICK_REQUIRE(a_rows > 0 && b_rows >= 0 && k > 0, "gemm_tc: bad sizes");
     if (b_rows == 0) return 0;
@@ -384,18 +465,46 @@ WICK_API int wick_gemm_tc(const void* a, long long a_total_rows, int a_rows, con
     if (stages > per_split) stages = per_split < 2 ? 2 : per_split;
     WICK_REQUIRE(stages >= 2, "gemm_tc: %d bytes of shared memory hold fewer than two stages of %d bytes", budget, stage_bytes);
     const int smem = stages * stage_bytes + 1024;
-    static int raised = 0;
-    if (smem > raised) {
-        WICK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024));
-        raised = 210 * 1024;
-    }
     GemmParams p;
     p.a_rows = a_rows; p.b_rows = b_rows; p.bn = bn; p.k_blocks = k_blocks; p.k_blocks_per_split = per_split;
     p.stages = stages; p.gated = gated; p.pair_offset = pair_offset; p.transposed = transposed; p.out_f32 = out_f32;
     p.ldo = ldo; p.split_stride = split_stride; p.out = out; p.status = status;
     p.a_static = a_static; p.b_static = b_static;
-    dim3 grid(ceil_div(a_rows, gated == 3 ? BM / 2 : BM), ceil_div(b_rows, bn), splits);
-    WICK_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "gemm_tc: grid limit");
-    WICK_CUDA(launch(gemm_tc_kernel, grid, dim3(NUM_THREADS), (size_t)smem, (cudaStream_t)stream, map_a, map_b, p));
-    return check_launch("gemm_tc");
+    p.grid_m = ceil_div(a_rows, gated == 3 ? BM / 2 : BM);
+    p.grid_n = ceil_div(b_rows, bn);
+    const long long total = (long long)p.grid_m * p.grid_n * splits;
+    WICK_REQUIRE(total < (1ll << 30), "gemm_tc: too many tiles");
+    p.total_tiles = (int)total;
+    // persistent blocks: as many as can be resident at once (148 SMs, one or two per SM by shared memory)
+    const int resident = 148 * ((smem + 12 * 1024) * 2 <= 227 * 1024 ? 2 : 1);
+    // Decode orientation (and anything that fits at once): one tile per block, so
+    // that a block starting while others still stream overlaps their drain.
+    // Prompt orientation with more tiles than resident blocks: persistent blocks.
+    const bool persistent = !transposed && p.total_tiles > resident;
+    WICK_REQUIRE(persistent || (p.grid_n <= 65535 && splits <= 65535), "gemm_tc: grid limit");
+    const dim3 grid = persistent ? dim3(resident) : dim3(p.grid_m, p.grid_n, splits);
+    // One instantiation per (persistent, pair mode, orientation, output type): a
+    // block of a decode step runs for a few microseconds, so the kernel it loads
+    // should hold nothing but its own path.
+#define WICK_GEMM_CASE(P, G, T, F)                                                                              \
+    if (persistent == P && gated == G && (transposed != 0) == T && (out_f32 != 0) == F) {                       \
+        static bool raised_##P##G##T##F = false;                                                                 \
+        if (!raised_##P##G##T##F) {                                                                              \
+            WICK_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<P, G, T, F>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                           210 * 1024));                                                         \
+            raised_##P##G##T##F = true;                                                                          \
+        }                                                                                                        \
+        WICK_CUDA(launch(gemm_tc_kernel<P, G, T, F>, grid, dim3(NUM_THREADS), (size_t)smem, (cudaStream_t)stream, \
+                         map_a, map_b, p));                                                                      \
+        return check_launch("gemm_tc");                                                                          \
+    }
+    WICK_GEMM_CASE(false, 0, true, true) WICK_GEMM_CASE(false, 0, true, false)
+    WICK_GEMM_CASE(false, 1, true, true) WICK_GEMM_CASE(false, 1, true, false)
+    WICK_GEMM_CASE(false, 3, true, true) WICK_GEMM_CASE(false, 3, true, false)
+    WICK_GEMM_CASE(false, 0, false, true) WICK_GEMM_CASE(false, 0, false, false)
+    WICK_GEMM_CASE(false, 2, false, true) WICK_GEMM_CASE(false, 2, false, false)
+    WICK_GEMM_CASE(true, 0, false, true) WICK_GEMM_CASE(true, 0, false, false)
+    WICK_GEMM_CASE(true, 2, false, true) WICK_GEMM_CASE(true, 2, false, false)
+#undef WICK_GEMM_CASE
+    return fail("gemm_tc: no kernel for pair mode %d with %s output", gated, transposed ? "transposed" : "row-major");
 }
