@@ -30,7 +30,12 @@ CONFIG_B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_s
 CONFIG_C = dict(architectures=["Qwen3ForCausalLM"], hidden_size=72, num_attention_heads=5, num_key_value_heads=1,
                 head_dim=48, intermediate_size=100, num_hidden_layers=1, vocab_size=333, max_position_embeddings=1024,
                 rope_theta=50000.0, rms_norm_eps=1e-6, tie_word_embeddings=False)
-CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C}
+# D: head_dim 64 with a group of 4, the sizes at which the bfloat16 path takes its
+# tensor-core attention kernels for decode as well as for prompts.
+CONFIG_D = dict(architectures=["Qwen3ForCausalLM"], hidden_size=128, num_attention_heads=8, num_key_value_heads=2,
+                head_dim=64, intermediate_size=256, num_hidden_layers=2, vocab_size=640, max_position_embeddings=1024,
+                rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=True)
+CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "D": CONFIG_D}
 
 _tmp_root = None
 

@@ -141,6 +141,31 @@ def test_long_decoding_over_several_splits(dtype):
     assert_logits_close(torch.cat(got), ref[200:], dtype, "decode from 200 to 512")
 
 
+@pytest.mark.parametrize("graphs", [False, True])
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_head_dim_64_prompt_then_long_decode_in_a_batch(dtype, graphs):
+    """Config D (head_dim 64, group of 4): in bfloat16 both attention kernels run
+    on the tensor cores.  Three sequences, prompts of unequal length, then 150
+    decoded tokens each (several decode splits, partial last pages)."""
+    name = "D"
+    eng = make_engine(name, dtype, use_graphs=graphs)
+    poison_all(eng)
+    lens = (3, 100, 260)
+    seqs = [random_tokens(vocab_of(name), n + 150, 60 + n) for n in lens]
+    refs = [plain_logits(name, s) for s in seqs]
+    slots = [eng.open_seq() for _ in seqs]
+    got = eng.step(slots, [s[:n] for s, n in zip(seqs, lens)], [[n - 1] for n in lens]).clone()
+    for i, n in enumerate(lens):
+        assert_logits_close(got[i], refs[i][n - 1], dtype, f"D prompt {i}")
+    for k in range(150):
+        got = eng.step(slots, [[s[n + k]] for s, n in zip(seqs, lens)]).clone()
+        if k % 7 == 0 or k > 140:
+            for i, n in enumerate(lens):
+                assert_logits_close(got[i], refs[i][n + k], dtype, f"D seq {i} decode {k}")
+    for s in slots:
+        eng.close_seq(s)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", NAMES)
 def test_first_tokens_of_a_sequence(name, dtype):

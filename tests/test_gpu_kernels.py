@@ -168,11 +168,13 @@ def test_qk_norm_rope_append_and_attention(ops, dtype, heads, kv_heads, hd):
     assert (kv2[page, :, :, :3].float() - kv[page, :, :, :3].float()).abs().max() < tol(dtype, 4)
 
 
+@pytest.mark.parametrize("hd", [32, 64])
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_attention_finds_one_far_key_among_hundreds(ops, dtype):
+def test_attention_finds_one_far_key_among_hundreds(ops, dtype, hd):
     """One key far back gets a score that dominates: the output must be its
-    value.  Random keys would hide a kernel that skips a page or a split."""
-    heads, kv_heads, hd = 4, 2, 32
+    value.  Random keys would hide a kernel that skips a page or a split.
+    (head_dim 64 in bfloat16 runs the tensor-core kernels.)"""
+    heads, kv_heads = 4, 2
     n = 700
     for far in (3, 64 * 4 + 1, 511, 640):
         torch.manual_seed(far)
@@ -181,7 +183,7 @@ def test_attention_finds_one_far_key_among_hundreds(ops, dtype):
         q = torch.randn(1, heads, hd) * 0.1
         k[far] = 0
         k[far, :, 0] = 8.0
-        q[0, :, 0] = 40.0                                   # score 40*8/sqrt(32) = 56 above all others
+        q[0, :, 0] = 40.0                                   # score 40*8/sqrt(hd) >= 40 above all others
         kv = _paged(13, kv_heads, hd, dtype)
         pages = [list(range(12, 12 - 11, -1))]              # 11 pages in descending order
         for p in range(n):

@@ -2,6 +2,8 @@
 // memory addresses, mbarriers with a bounded wait, and the untiled bulk copy.
 #pragma once
 
+#include <cuda.h>
+
 #include "common.cuh"
 
 namespace wick {
@@ -54,6 +56,50 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
+}
+
+// Tiled TMA load of one box of a 2-D tensor map; x is the inner coordinate (its
+// byte offset must be a multiple of 16), completion is counted on the mbarrier.
+__device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint64_t* bar, void* dst, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// A [rows, cols] bfloat16 matrix, row-major, as a TMA descriptor with boxes of
+// box_rows x 64 elements (128 bytes, the width of the 128-byte swizzle).
+inline int make_bf16_map(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int box_rows, const char* who) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    WICK_REQUIRE(fn != nullptr, "%s: the driver does not provide cuTensorMapEncodeTiled", who);
+    WICK_REQUIRE(((uintptr_t)ptr & 15) == 0, "%s: operand is not 16-byte aligned", who);
+    WICK_REQUIRE(cols % 8 == 0, "%s: inner size %lld is not a multiple of 8 (16-byte rows)", who, (long long)cols);
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    WICK_REQUIRE(r == CUDA_SUCCESS, "%s: cuTensorMapEncodeTiled failed with code %d (rows %lld, cols %lld, box %d)", who,
+                 (int)r, (long long)rows, (long long)cols, box_rows);
+    return 0;
 }
 
 }  // namespace wick

@@ -48,13 +48,15 @@ class Workspace:
         self.buffers: Dict[str, torch.Tensor] = {}
         self.frozen = False
 
-    def get(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
+    def get(self, name: str, numel: int, dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
+        """zero: the buffer is zero when it is made (its users leave it zero)."""
         b = self.buffers.get(name)
         if b is None or b.numel() < numel or b.dtype != dtype:
             if self.frozen:
                 raise RuntimeError(f"scratch buffer {name} would have to grow to {numel} elements while a CUDA "
                                    f"graph is being captured")
-            b = self.buffers[name] = torch.empty(max(numel, 1), dtype=dtype, device=self.device)
+            make = torch.zeros if zero else torch.empty
+            b = self.buffers[name] = make(max(numel, 1), dtype=dtype, device=self.device)
         return b
 
 

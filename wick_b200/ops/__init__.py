@@ -85,7 +85,7 @@ def _simt() -> _Lib:
     return lib
 
 
-ATTN_SOURCES = ["attn.cu", "attn_decode.cu", "attn_prompt_mma.cu"]
+ATTN_SOURCES = ["attn.cu", "attn_decode.cu", "attn_decode_mma.cu", "attn_prompt_mma.cu"]
 
 
 def _attn(head_dim: int) -> _Lib:
@@ -104,7 +104,8 @@ def _attn(head_dim: int) -> _Lib:
 # accumulator), 4 decode attention (its bulk copies).
 _status: Optional[torch.Tensor] = None
 _STATUS_TEXT = {1: "gemm_tc: a free shared-memory stage", 2: "gemm_tc: a TMA copy", 3: "gemm_tc: the accumulator",
-                4: "attention decode: its bulk copies"}
+                4: "attention decode: its bulk copies", 5: "gemm_tc: a free accumulator",
+                6: "attention decode (tensor cores): its TMA copies"}
 
 
 def status_tensor(device) -> torch.Tensor:
@@ -315,14 +316,23 @@ def attention_prompt(q: torch.Tensor, kv: torch.Tensor, batch, scale: float,
 _decode_split: Dict[tuple, int] = {}
 
 
+def attention_decode_kind(head_dim: int, dtype: torch.dtype, plain: bool = False) -> str:
+    """Which decode kernel runs: ``mma`` (tensor cores: bfloat16, head sizes that are
+    64 or 128), ``fast`` (CUDA cores from bulk-copied tiles) or ``plain``."""
+    if plain:
+        return "plain"
+    return "mma" if dtype == torch.bfloat16 and head_dim in (64, 128) else "fast"
+
+
 def attention_decode_split(head_dim: int, dtype: torch.dtype, plain: bool = False) -> int:
     """Cached positions handled by one block of the decode kernel."""
-    key = (head_dim, dtype, plain)
+    kind = attention_decode_kind(head_dim, dtype, plain)
+    key = (head_dim, dtype, kind)
     v = _decode_split.get(key)
     if v is None:
         lib = _attn(head_dim)._lib
-        name = "wick_attn_decode_plain_split" if plain else \
-            f"wick_attn_decode_split_{'bf16' if dtype == torch.bfloat16 else 'f32'}"
+        name = {"plain": "wick_attn_decode_plain_split", "mma": "wick_attn_decode_mma_split",
+                "fast": f"wick_attn_decode_split_{'bf16' if dtype == torch.bfloat16 else 'f32'}"}[kind]
         f = getattr(lib, name)
         f.restype = ctypes.c_int
         f.argtypes = []
@@ -341,8 +351,8 @@ def attention_decode(q: torch.Tensor, kv: torch.Tensor, batch, scale: float, scr
                      plain: bool = False) -> torch.Tensor:
     """One new token per sequence.  scratch: float32, at least
     :func:`attention_decode_scratch_floats` elements; it holds the per-split
-    partial sums between the two kernels.  plain: the form without shared-memory
-    staging (the fast form's twin)."""
+    partial results between the two kernels.  plain: the form without
+    shared-memory staging."""
     _cuda("q", q)
     n, n_heads, hd = q.shape
     _cuda("kv", kv, q.dtype)
@@ -355,12 +365,18 @@ def attention_decode(q: torch.Tensor, kv: torch.Tensor, batch, scale: float, scr
         out = torch.empty_like(q)
     _cuda("out", out, q.dtype, q.shape)
     mk = batch.max_kv_len if max_kv_len is None else max_kv_len
-    if plain:
+    kind = attention_decode_kind(hd, q.dtype, plain)
+    if kind == "plain":
         _attn(hd).call(f"wick_attn_decode_plain_{_dt(q)}", "pppplpiipiiifp", _p(q), _p(kv), _p(out),
                        _p(scratch), scratch.numel(), _p(batch.kv_len), n, mk, _p(batch.page_table),
                        batch.table_width, n_heads, n_kv, float(scale), _stream(), kernels=2)
-    else:
+    elif kind == "fast":
         _attn(hd).call(f"wick_attn_decode_{_dt(q)}", "pppplpiipiiifpp", _p(q), _p(kv), _p(out),
+                       _p(scratch), scratch.numel(), _p(batch.kv_len), n, mk, _p(batch.page_table),
+                       batch.table_width, n_heads, n_kv, float(scale), _p(status_tensor(q.device)), _stream(),
+                       kernels=2)
+    else:
+        _attn(hd).call("wick_attn_decode_mma_bf16", "pplpplpiipiiifpp", _p(q), _p(kv), kv.shape[0], _p(out),
                        _p(scratch), scratch.numel(), _p(batch.kv_len), n, mk, _p(batch.page_table),
                        batch.table_width, n_heads, n_kv, float(scale), _p(status_tensor(q.device)), _stream(),
                        kernels=2)
