@@ -35,7 +35,13 @@ CONFIG_C = dict(architectures=["Qwen3ForCausalLM"], hidden_size=72, num_attentio
 CONFIG_D = dict(architectures=["Qwen3ForCausalLM"], hidden_size=128, num_attention_heads=8, num_key_value_heads=2,
                 head_dim=64, intermediate_size=256, num_hidden_layers=2, vocab_size=640, max_position_embeddings=1024,
                 rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=True)
-CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "D": CONFIG_D}
+# R: one layer with the real widths of Qwen3-8B (hidden 4096, 32 heads over 8 kv
+# heads of 128, intermediate 12288) and a vocabulary that is no multiple of the
+# kernels' tile sizes.
+CONFIG_R = dict(architectures=["Qwen3ForCausalLM"], hidden_size=4096, num_attention_heads=32, num_key_value_heads=8,
+                head_dim=128, intermediate_size=12288, num_hidden_layers=1, vocab_size=20011,
+                max_position_embeddings=4096, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False)
+CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "D": CONFIG_D, "R": CONFIG_R}
 
 _tmp_root = None
 

@@ -241,3 +241,27 @@ def test_model_with_random_weights_drawn_on_the_device():
     s = eng.open_seq()
     out = eng.step([s], [[1, 2, 3]])
     assert out.shape == (1, 1000) and torch.isfinite(out).all() and out.abs().max() > 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_real_layer_widths_of_qwen3_8b(dtype):
+    """One layer at the real widths (config R): a prompt whole, a second prompt in
+    the same batch, then decoded tokens — so that the kernels run with their real
+    tile counts, splits and strides.  float32 must match the plain implementation
+    to 1e-4 here too."""
+    name = "R"
+    eng = make_engine(name, dtype, max_tokens=1024)
+    poison_all(eng)
+    seqs = [random_tokens(vocab_of(name), n, 900 + n) for n in (150, 37)]
+    refs = [plain_logits(name, s) for s in seqs]
+    slots = [eng.open_seq() for _ in seqs]
+    heads = [len(s) - 6 for s in seqs]
+    got = eng.step(slots, [s[:h] for s, h in zip(seqs, heads)], [[0, h // 2, h - 1] for h in heads]).clone()
+    for i, h in enumerate(heads):
+        assert_logits_close(got[3 * i:3 * i + 3], refs[i][[0, h // 2, h - 1]], dtype, f"R prompt {i}")
+    for k in range(6):
+        got = eng.step(slots, [[s[h + k]] for s, h in zip(seqs, heads)]).clone()
+        for i, h in enumerate(heads):
+            assert_logits_close(got[i], refs[i][h + k], dtype, f"R seq {i} decode {k}")
+    for s in slots:
+        eng.close_seq(s)
