@@ -337,6 +337,27 @@ def test_gemm_tensor_core_both_ways_round(t, n, k, gated):
     assert (got32 - twin).abs().max() < (1e-2 if gated else 2e-4) * max(1.0, ref.abs().max())   # gated twin: bf16 out
 
 
+@pytest.mark.parametrize("t, n, k, gated", [(256, 256, 64, False), (257, 100, 72, True), (700, 520, 200, False),
+                                            (1000, 333, 328, True), (2100, 1536, 1024, False)])
+def test_gemm_tensor_core_single_blocks_and_pairs(monkeypatch, t, n, k, gated):
+    """From 256 tokens on two thread blocks share a 256 x 256 tile; the kernel for
+    single blocks takes the same sizes.  Both against a float64 product."""
+    from wick_b200.ops import gemm_tc as G
+    torch.manual_seed(t + n + k)
+    x = torch.randn(t, k).bfloat16()
+    w = (torch.randn(2 * n if gated else n, k) / math.sqrt(k)).bfloat16()
+    ref = _tc_ref(x, w, gated)
+    plan = G.plan_for(dev(w), gated)
+    assert t >= G.PAIR_MIN
+    for pair_min in (G.PAIR_MIN, 1 << 30):
+        monkeypatch.setattr(G, "PAIR_MIN", pair_min)
+        got32 = plan.forward(dev(x), torch.float32)
+        got16 = plan.forward(dev(x), torch.bfloat16)
+        G.check_status()
+        assert (got32.cpu() - ref).abs().max() < 2e-4 * max(1.0, ref.abs().max()), pair_min
+        assert (got16.float().cpu() - ref).abs().max() < 1e-2 * max(1.0, ref.abs().max()), pair_min
+
+
 def ops_gemm_simt(x, w, gated):
     from wick_b200 import ops
     return ops.gemm_simt(x, w, torch.bfloat16 if gated else torch.float32, gated=gated).float()

@@ -11,6 +11,8 @@ which way round the kernel runs:
   depends on the matrix alone, never on the batch.
 * more tokens: the tokens are the 128-row operand, weight tiles are 256 rows
   (128 + 128 for a gated pair) wide.
+* 256 tokens and more: the kernel of ``csrc/gemm_tc2.cu``, in which two thread
+  blocks on neighbouring SMs share one 256 x 256 tile.
 
 Inner sizes that are no multiple of 8 (rows that are no multiple of 16 bytes
 cannot be fetched by TMA) have no plan; the caller then uses the CUDA-core kernel.
@@ -24,12 +26,16 @@ import torch
 from . import KernelError, _Lib, _libs, _p, _stream, check_status, status_tensor  # noqa: F401
 
 SMALL = 64                  # up to this many tokens the weights are the 128-row operand
+PAIR_MIN = 256              # from this many tokens on, pairs of thread blocks share 256 x 256 tiles
 N_SMS = 148
+
+SOURCES = ["gemm_tc.cu", "gemm_tc2.cu"]
+
 
 def _lib() -> _Lib:
     lib = _libs.get("gemm_tc")
     if lib is None:
-        lib = _libs["gemm_tc"] = _Lib("wick_gemm_tc", ["gemm_tc.cu"])
+        lib = _libs["gemm_tc"] = _Lib("wick_gemm_tc", SOURCES)
     return lib
 
 
@@ -52,6 +58,21 @@ def gemm_tc(a: torch.Tensor, a_rows: int, b: torch.Tensor, b_rows: int, *, bn: i
                 pair_offset, 1 if transposed else 0, 1 if out.dtype == torch.float32 else 0, 1 if a_static else 0,
                 1 if b_static else 0, _p(out), ldo, splits,
                 split_stride, max_smem, _p(st), _stream())
+
+
+def gemm_tc_pair(a: torch.Tensor, b: torch.Tensor, b_rows: int, *, out: torch.Tensor, ldo: int, gated: bool = False,
+                 pair_offset: int = 0) -> None:
+    """The kernel for pairs of thread blocks (see ``wick_gemm_tc2`` in gemm_tc2.cu): out[m, n] = a[m] . b[n]."""
+    for nm, t in (("a", a), ("b", b)):
+        if not (t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous() and t.dim() == 2):
+            raise KernelError(f"gemm_tc_pair: {nm} must be a contiguous 2-D bfloat16 CUDA tensor")
+    if a.shape[1] != b.shape[1]:
+        raise KernelError(f"gemm_tc_pair: inner sizes differ: {a.shape[1]} and {b.shape[1]}")
+    if out.dtype not in (torch.float32, torch.bfloat16) or not out.is_contiguous():
+        raise KernelError("gemm_tc_pair: out must be contiguous float32 or bfloat16")
+    st = status_tensor(a.device)
+    _lib().call("wick_gemm_tc2", "pipliiiiiplpp", _p(a), a.shape[0], _p(b), b.shape[0], b_rows, a.shape[1],
+                1 if gated else 0, pair_offset, 1 if out.dtype == torch.float32 else 0, _p(out), ldo, _p(st), _stream())
 
 
 def _ceil16(n: int) -> int:
@@ -98,6 +119,8 @@ class Plan:
             gemm_tc(self.w, self.n_out, x, t, bn=_ceil16(t), out=out, ldo=self.n_out,
                     gated=3 if self.gated else 0, pair_offset=self.n_out, transposed=True, splits=splits,
                     split_stride=t * self.n_out, max_smem=100 * 1024, a_static=True)
+        elif t >= PAIR_MIN and splits == 1:
+            gemm_tc_pair(x, self.w, self.n_out, out=out, ldo=self.n_out, gated=self.gated, pair_offset=self.n_out)
         else:
             bn = min(128 if self.gated else 256, _ceil16(self.n_out))
             gemm_tc(x, t, self.w, self.n_out, bn=bn, out=out, ldo=self.n_out, gated=2 if self.gated else 0,
