@@ -4,7 +4,11 @@
   put into a model next to attention layers, built, loaded and stepped — prompt,
   decode, captured decode, batches, slot reuse — without touching the package;
 * a run order that names a layer twice and lets a layer read another layer's
-  cache.
+  cache;
+* a feed-forward with routing (one expert of several per token, chosen by
+  float32 router logits) and a position encoding that the fused kernel does not
+  know (rotation of neighbouring pairs with positions divided by a factor), in
+  different layers of one model.
 
 The toys use torch operations; they are test fixtures, not models."""
 import dataclasses
@@ -16,7 +20,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 import wick_b200 as wick  # noqa: E402
-from wick_b200.parts.base import CacheNeed, Mixer, TensorSpec, register_part  # noqa: E402
+from wick_b200.parts.base import CacheNeed, FeedForward, Mixer, Position, TensorSpec, register_part  # noqa: E402
 from helpers import CONFIG_A, CONFIG_B, assert_logits_close, random_tokens, tmp_root  # noqa: E402
 from plain import qwen3_plain as P  # noqa: E402
 
@@ -168,3 +172,151 @@ def test_a_layer_named_twice_and_a_layer_reading_anothers_cache(dtype):
     got += [eng.step([s], [[t]]).clone() for t in toks[70:]]
     assert_logits_close(torch.cat(got), ref, dtype, "looped schedule")
     assert eng.model.weight_bytes_per_step() > 0
+
+
+# ---------------------------------------------------------------------------
+class RoutedExperts(FeedForward):
+    """Each token goes to the one expert with the largest router logit (the first
+    of equals); out = logit-softmax weight of that expert * W2 relu(W1 x)."""
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.width, self.inner, self.experts = int(params["width"]), int(params["inner"]), int(params["experts"])
+
+    def tensor_specs(self):
+        specs = [TensorSpec("router.weight", (self.experts, self.width))]
+        for e in range(self.experts):
+            specs += [TensorSpec(f"experts.{e}.w1.weight", (self.inner, self.width)),
+                      TensorSpec(f"experts.{e}.w2.weight", (self.width, self.inner))]
+        return specs
+
+    def load(self, fetch):
+        self.router = self.ctx.hold(fetch("router.weight"), "matrix")
+        self.w1 = torch.stack([self.ctx.hold(fetch(f"experts.{e}.w1.weight"), "matrix") for e in range(self.experts)])
+        self.w2 = torch.stack([self.ctx.hold(fetch(f"experts.{e}.w2.weight"), "matrix") for e in range(self.experts)])
+
+    def forward(self, x, batch):
+        xf = x.float()
+        logits = xf @ self.router.float().T                                  # router logits in float32
+        probs = torch.softmax(logits, dim=-1)
+        choice = logits.argmax(dim=-1)
+        gate = probs.gather(1, choice[:, None])
+        h = torch.relu(torch.bmm(self.w1.float()[choice], xf[:, :, None]))    # [n, inner, 1]
+        y = torch.bmm(self.w2.float()[choice], h)[:, :, 0] * gate
+        return y.unsqueeze(0)
+
+
+class NeighbourPairRotary(Position):
+    """Pairs (2i, 2i+1) of every head rotated by (position / factor) * theta^(-2i/d)."""
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        d = int(params["head_dim"])
+        self.factor = float(params["factor"])
+        self.inv_freq = torch.tensor([float(params["theta"]) ** (-2.0 * i / d) for i in range(d // 2)],
+                                     dtype=torch.float32, device=ctx.device)
+
+    def apply(self, q, k, positions):
+        angle = (positions.float() / self.factor)[:, None] * self.inv_freq[None, :]
+        cos, sin = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
+        for t in (q, k):
+            a, b = t[..., 0::2].clone(), t[..., 1::2].clone()
+            t[..., 0::2] = a * cos - b * sin
+            t[..., 1::2] = b * cos + a * sin
+
+
+register_part("ffn", "toy_routed", RoutedExperts)
+register_part("position", "toy_neighbour_pairs", NeighbourPairRotary)
+
+TOY_EXPERTS, TOY_INNER, TOY_FACTOR = 3, 40, 4.0
+
+
+def build_routed_spec(cfg):
+    spec = wick.get_architecture("qwen3").build_spec(cfg)
+    layers = list(spec.layers)
+    pos = wick.PartSpec("toy_neighbour_pairs", {"head_dim": cfg.head_dim, "theta": cfg.rope_theta, "factor": TOY_FACTOR})
+    for i in range(len(layers)):
+        L = layers[i]
+        if i % 2 == 0:                                         # even layers: the other position encoding
+            L = dataclasses.replace(L, mixer=wick.PartSpec(L.mixer.kind, {**L.mixer.params, "position": pos}))
+        else:                                                  # odd layers: the routed feed-forward
+            L = dataclasses.replace(
+                L, ffn=wick.PartSpec("toy_routed", {"width": cfg.hidden_size, "inner": TOY_INNER, "experts": TOY_EXPERTS}),
+                names={**L.names, "ffn": "moe."})
+        layers[i] = L
+    return dataclasses.replace(spec, layers=tuple(layers))
+
+
+wick.register_architecture(wick.Architecture(("ToyRoutedForCausalLM",), wick.Qwen3Config, build_routed_spec))
+
+
+def plain_routed_forward(cfg, w, tokens):
+    toks = torch.as_tensor(tokens)
+    T = len(tokens)
+    H, KV, D = cfg["heads"], cfg["kv_heads"], cfg["head_dim"]
+    x = w["model.embed_tokens.weight"][toks]
+    pos = torch.arange(T)
+    for layer in range(cfg["layers"]):
+        p = f"model.layers.{layer}."
+        xn = P.rms_norm(x, w[p + "input_layernorm.weight"], cfg["eps"])
+        if layer % 2 == 0:
+            q = P.rms_norm((xn @ w[p + "self_attn.q_proj.weight"].T).view(T, H, D), w[p + "self_attn.q_norm.weight"], cfg["eps"])
+            k = P.rms_norm((xn @ w[p + "self_attn.k_proj.weight"].T).view(T, KV, D), w[p + "self_attn.k_norm.weight"], cfg["eps"])
+            v = (xn @ w[p + "self_attn.v_proj.weight"].T).view(T, KV, D)
+            inv = torch.tensor([cfg["theta"] ** (-2.0 * i / D) for i in range(D // 2)], dtype=torch.float32)
+            ang = (pos.float() / TOY_FACTOR)[:, None] * inv[None, :]
+            c, s_ = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+
+            def rot(t):
+                a, b = t[..., 0::2], t[..., 1::2]
+                return torch.stack([a * c - b * s_, b * c + a * s_], dim=-1).reshape(t.shape)
+            d = P.causal_attention(rot(q), rot(k), v).reshape(T, H * D) @ w[p + "self_attn.o_proj.weight"].T
+        else:
+            d, _ = P.attention_block(xn, w, p, cfg, pos)
+        x = x + d
+        xn = P.rms_norm(x, w[p + "post_attention_layernorm.weight"], cfg["eps"])
+        if layer % 2 == 1:
+            logits = xn @ w[p + "moe.router.weight"].T
+            rows = []
+            for t in range(T):
+                e = int(P.argmax_first(logits[t]))
+                g = P.softmax_rows(logits[t:t + 1])[0, e]
+                h = torch.relu(w[p + f"moe.experts.{e}.w1.weight"] @ xn[t])
+                rows.append((w[p + f"moe.experts.{e}.w2.weight"] @ h) * g)
+            x = x + torch.stack(rows)
+        else:
+            x = x + P.swiglu(xn, w, p)
+    xn = P.rms_norm(x, w["model.norm.weight"], cfg["eps"])
+    head = w["model.embed_tokens.weight"] if cfg["tied"] else w["lm_head.weight"]
+    return xn @ head.T
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_a_routed_feed_forward_and_another_position_encoding(graphs):
+    cfg = wick.config_from_json(dict(CONFIG_B, architectures=["ToyRoutedForCausalLM"], num_hidden_layers=4))
+    d = os.path.join(tmp_root(), "toy-routed")
+    wick.write_random_model(cfg, 11, d, dtype=torch.float32, std=0.08)
+    eng = wick.Engine.from_dir(d, dtype="float32", max_tokens=512, use_graphs=graphs)
+    table = eng.model.tensor_table()
+    assert "model.layers.1.moe.experts.2.w2.weight" in table and "model.layers.1.mlp.gate_proj.weight" not in table
+    assert "model.layers.0.mlp.gate_proj.weight" in table
+    pc, pw = P.read_model_dir(d)
+    seqs = [random_tokens(1000, n, 900 + n) for n in (70, 13, 5)]
+    refs = [plain_routed_forward(pc, pw, s) for s in seqs]
+    used = set()
+    for s in seqs:                                             # the router does choose: more than one expert is in use
+        x = pw["model.embed_tokens.weight"][torch.as_tensor(s)]
+        used |= set((x @ pw["model.layers.1.moe.router.weight"].T).argmax(-1).tolist())
+    assert len(used) > 1
+    slots = [eng.open_seq() for _ in seqs]
+    got = eng.step(slots, [s[:-4] for s in seqs], [list(range(len(s) - 4)) for s in seqs]).clone()
+    off = 0
+    for s, r in zip(seqs, refs):
+        assert_logits_close(got[off:off + len(s) - 4], r[:len(s) - 4], "float32", "routed prompt")
+        off += len(s) - 4
+    for k in range(4, 0, -1):
+        got = eng.step(slots, [[s[-k]] for s in seqs]).clone()
+        for i, (s, r) in enumerate(zip(seqs, refs)):
+            assert_logits_close(got[i], r[len(s) - k], "float32", "routed decode")
+    for sl in slots:
+        eng.close_seq(sl)

@@ -153,22 +153,22 @@ class GQAttention(Mixer):
         return self.qkv.weight_bytes() + self.o.weight_bytes() + (2 * self.head_dim * 4 if self.q_norm else 0)
 
     def forward(self, x, batch, cache, write_cache):
-        qkv = self.qkv.forward_delta(x)                  # float32 partial sums [splits, n, q_dim + 2 kv_dim]
         inv_freq = self.position.rotary_inv_freq()
-        cos = sin = None
-        if inv_freq is not None:
-            cos, sin = self.position.tables(batch)
-        q = ops.qk_norm_rope_append(
-            qkv, self.heads, self.kv_heads, self.head_dim,
-            q_weight=self.q_norm.weight if self.q_norm else None,
-            k_weight=self.k_norm.weight if self.k_norm else None,
-            eps=self.q_norm.eps if self.q_norm else 0.0,
-            cos=cos, sin=sin, kv=cache.kv, page_table=batch.page_table,
-            seq_of_token=batch.seq_of_token, positions=batch.positions, write_kv=write_cache,
-            dtype=self.ctx.dtype)
         if inv_freq is None and not isinstance(self.position, NoPosition):
-            raise NotImplementedError("a position encoding that is not a half-split rotation has to be applied "
-                                      "before the cache append; give the mixer a kernel for it")
+            q = self._encode_unfused(x, batch, cache, write_cache)
+        else:
+            qkv = self.qkv.forward_delta(x)              # float32 partial sums [splits, n, q_dim + 2 kv_dim]
+            cos = sin = None
+            if inv_freq is not None:
+                cos, sin = self.position.tables(batch)
+            q = ops.qk_norm_rope_append(
+                qkv, self.heads, self.kv_heads, self.head_dim,
+                q_weight=self.q_norm.weight if self.q_norm else None,
+                k_weight=self.k_norm.weight if self.k_norm else None,
+                eps=self.q_norm.eps if self.q_norm else 0.0,
+                cos=cos, sin=sin, kv=cache.kv, page_table=batch.page_table,
+                seq_of_token=batch.seq_of_token, positions=batch.positions, write_kv=write_cache,
+                dtype=self.ctx.dtype)
         if batch.is_decode:
             need = ops.attention_decode_scratch_floats(batch.n_seqs, self.heads, self.head_dim, batch.kv_bound,
                                                        self.ctx.dtype)
@@ -178,6 +178,28 @@ class GQAttention(Mixer):
         else:
             att = ops.attention_prompt(q, cache.kv, batch, self.scale)
         return self.o.forward_delta(att.view(batch.n_tokens, self.q_dim))
+
+
+    def _encode_unfused(self, x, batch, cache, write_cache):
+        """The way for a position encoding that the fused kernel does not know:
+        project, norm q and k per head, let the encoding's own ``apply`` work on
+        float32 q [n, heads, d] and k [n, kv_heads, d], then append k and v to the
+        cache.  Slower than the fused kernel by a few copies."""
+        n = x.shape[0]
+        qkv = self.qkv.forward(x, torch.float32)
+        q = qkv[:, :self.q_dim].reshape(n * self.heads, self.head_dim)
+        k = qkv[:, self.q_dim:self.q_dim + self.kv_dim].reshape(n * self.kv_heads, self.head_dim)
+        v = qkv[:, self.q_dim + self.kv_dim:]
+        if self.q_norm is not None:
+            q = self.q_norm.forward(q, torch.float32)
+            k = self.k_norm.forward(k, torch.float32)
+        q, k = q.view(n, self.heads, self.head_dim), k.view(n, self.kv_heads, self.head_dim)
+        self.position.apply(q, k, batch.positions)
+        encoded = torch.cat([q.view(n, -1), k.view(n, -1), v], dim=1).to(self.ctx.dtype)
+        return ops.qk_norm_rope_append(
+            encoded, self.heads, self.kv_heads, self.head_dim, q_weight=None, k_weight=None, eps=0.0, cos=None,
+            sin=None, kv=cache.kv, page_table=batch.page_table, seq_of_token=batch.seq_of_token,
+            positions=batch.positions, write_kv=write_cache)
 
 
 # ---------------------------------------------------------------------------
