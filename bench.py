@@ -107,14 +107,14 @@ def reference_arm():
     return 0
 
 
-def device_timed_decode(torch, wick, ops, eng, batch, steps, warmup, vocab, seed):
-    """W + K decode steps of `batch` sequences after 512-token prompts; returns
+def device_timed_decode(torch, wick, ops, eng, batch, steps, warmup, vocab, seed, prompt_len=PROMPT):
+    """W + K decode steps of `batch` sequences after prompts of prompt_len tokens; returns
     (ms per step over the K timed steps, kernels launched in them, kv tokens read)."""
     g = torch.Generator().manual_seed(seed)
-    prompts = [torch.randint(0, vocab, (PROMPT,), generator=g).tolist() for _ in range(batch)]
+    prompts = [torch.randint(0, vocab, (prompt_len,), generator=g).tolist() for _ in range(batch)]
     slots = [eng.open_seq() for _ in prompts]
     for s in slots:
-        eng.cache.reserve(s, min(CONTEXT, PROMPT + warmup + steps + 1))
+        eng.cache.reserve(s, min(CONTEXT, prompt_len + warmup + steps + 1))
     # prompts in chunks of at most 8 sequences to bound activation memory
     tok = []
     for i in range(0, batch, 8):
@@ -148,6 +148,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--prompt-len", type=int, default=PROMPT, help="tokens of each prompt before the timed decode steps")
     ap.add_argument("--skip-points", action="store_true", help="no batch 1 / 64 runs")
     ap.add_argument("--skip-e2e", action="store_true", help="no run through the Python entry point")
     ap.add_argument("--skip-prefill", action="store_true")
@@ -160,7 +161,7 @@ def main() -> int:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not built")
         return 2
     warmup = max(args.warmup, 3)
-    steps = max(1, min(args.steps, CONTEXT - PROMPT - warmup - 2))
+    steps = max(1, min(args.steps, CONTEXT - args.prompt_len - warmup - 2))
 
     import torch
 
@@ -174,7 +175,7 @@ def main() -> int:
         cfg_json["num_hidden_layers"] = args.layers
     cfg = wick.config_from_json(cfg_json)
     max_batch = max(args.batch, 1 if args.skip_points else 64)
-    per_seq = (PROMPT + 3 + steps + 64 + 63) // 64 * 64
+    per_seq = (args.prompt_len + 3 + steps + 64 + 63) // 64 * 64
     max_tokens = max(max_batch * per_seq, PREFILL + 64)
     t0 = time.time()
     eng = wick.Engine.from_config(cfg, seed=0, dtype="bfloat16", max_tokens=max_tokens,
@@ -190,7 +191,7 @@ def main() -> int:
         if args.skip_decode:
             ms, launches, kv_tokens = float("nan"), 0, 0
         else:
-            ms, launches, kv_tokens = device_timed_decode(torch, wick, ops, eng, args.batch, steps, warmup, vocab, 1)
+            ms, launches, kv_tokens = device_timed_decode(torch, wick, ops, eng, args.batch, steps, warmup, vocab, 1, args.prompt_len)
     value = args.batch * 1e3 / ms
     step_bytes = weight_bytes + kv_tokens * kv_bytes_per_token
     achieved = step_bytes / (ms * 1e-3) / 1e9
@@ -198,7 +199,7 @@ def main() -> int:
     # ---- decode through the Python entry point, host tokens in and out ----
     e2e_value = None
     g = torch.Generator().manual_seed(2)
-    prompts = [torch.randint(0, vocab, (PROMPT,), generator=g).tolist() for _ in range(args.batch)]
+    prompts = [torch.randint(0, vocab, (args.prompt_len,), generator=g).tolist() for _ in range(args.batch)]
     opts = wick.GenOptions(max_tokens=steps + 1, sampler=wick.SamplerConfig.greedy(), context=CONTEXT,
                            max_batch=args.batch)
     if not args.skip_e2e and not args.skip_decode:
@@ -239,18 +240,18 @@ def main() -> int:
     points = {}
     if not args.skip_points and not args.skip_decode:
         for b in (1, 64):
-            pms_b, _, _ = device_timed_decode(torch, wick, ops, eng, b, min(steps, 64), warmup, vocab, 10 + b)
+            pms_b, _, _ = device_timed_decode(torch, wick, ops, eng, b, min(steps, 64), warmup, vocab, 10 + b, args.prompt_len)
             points[f"decode_b{b}"] = b * 1e3 / pms_b
 
     line = {
-        "metric": "Qwen3-8B bf16 decode tok/s @ bs 8 (512-token prompts, context 4096)",
+        "metric": f"Qwen3-8B bf16 decode tok/s @ bs {args.batch} ({args.prompt_len}-token prompts, context {CONTEXT})",
         "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: seeded random weights N(0,0.02), seeded uniform random token ids",
         "config": {"model": "Qwen3-8B sizes", "layers": len(eng.spec.schedule), "layers_of_config": full_layers,
                    "hidden": c.hidden_size, "heads": c.num_attention_heads, "kv_heads": c.num_key_value_heads,
                    "head_dim": c.head_dim, "intermediate": c.intermediate_size, "vocab": vocab,
-                   "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT, "parallelism": "none",
+                   "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": args.prompt_len, "parallelism": "none",
                    "l2": "inputs larger than L2 (weights per step far exceed 126 MB)",
                    "peaks": pk["source"]},
         "clocks": clk.result,

@@ -147,6 +147,9 @@ def test_qk_norm_rope_append_and_attention(ops, dtype, heads, kv_heads, hd):
     assert torch.isfinite(out.float()).all(), "a NaN from an unwritten cache position leaked"
     assert (out.float().cpu() - ref_o).abs().max() < tol(dtype, 2)
     assert (out_plain.float().cpu() - ref_o).abs().max() < tol(dtype, 2), "the CUDA-core twin"
+    if dtype == torch.bfloat16 and hd <= 128:
+        out_mma = ops.attention_prompt(q, kv, fb, 1 / math.sqrt(hd), kind="mma")
+        assert (out_mma.float().cpu() - ref_o).abs().max() < tol(dtype, 2), "the mma.sync form"
     # decode attention: the last token of each sequence alone
     fd = FakeBatch([1, 1], [t - 1 for t in totals], pages).sb
     last = torch.tensor([q_lens[0] - 1, sum(q_lens) - 1], device="cuda")
@@ -201,6 +204,59 @@ def test_attention_finds_one_far_key_among_hundreds(ops, dtype, hd):
         fp = FakeBatch([5], [n - 5], pages).sb
         outp = ops.attention_prompt(dev(qs.to(dtype)), kv, fp, 1 / math.sqrt(hd)).float().cpu()
         assert (outp[4] - want).abs().max() < 1e-2, f"prompt kernel missed key {far}"
+
+
+@pytest.mark.parametrize("heads, kv_heads, hd", [(4, 2, 128), (6, 3, 64), (3, 1, 128)])
+def test_prompt_attention_on_tcgen05(ops, heads, kv_heads, hd):
+    """The tcgen05 prompt kernel against the plain parts and its two twins: several
+    sequences with and without a cached prefix, blocks of 128 rows that end inside a
+    sequence, lengths around the 128-key step, scrambled pages, NaN wherever the cache
+    holds no token, and scores whose maximum jumps far up late in a row (so that the
+    accumulator in tensor memory is rescaled) and early in a row (so that it is not)."""
+    assert ops.attention_prompt_kind(hd, torch.bfloat16) == "tc"
+    torch.manual_seed(hd + heads)
+    q_lens, starts = [300, 128, 1, 129, 257], [77, 0, 500, 127, 0]
+    totals = [s + q for s, q in zip(starts, q_lens)]
+    n_pages = sum((t + 63) // 64 for t in totals) + 1
+    perm = (torch.randperm(n_pages - 1) + 1).tolist()
+    pages, o = [], 0
+    for t in totals:
+        n = (t + 63) // 64
+        pages.append(perm[o:o + n])
+        o += n
+    kv = _paged(n_pages, kv_heads, hd, torch.bfloat16)          # NaN everywhere
+    ks, vs, qs = [], [], []
+    for b, t in enumerate(totals):
+        k = torch.randn(t, kv_heads, hd)
+        v = torch.randn(t, kv_heads, hd)
+        q = torch.randn(q_lens[b], heads, hd)
+        if t > 200:                                              # one key that dominates from position 190 on
+            k[190] *= 0.0
+            k[190, :, 1] = 30.0
+            q[:, :, 1] = q[:, :, 1].abs() * 0 + 12.0
+        if b == 4:                                               # and one at position 2
+            k[2] *= 0.0
+            k[2, :, 3] = 30.0
+            q[:, :, 3] = 9.0
+        k, v, q = k.bfloat16(), v.bfloat16(), q.bfloat16()
+        for p in range(t):
+            kv[pages[b][p // 64], 0, :, p % 64] = k[p].cuda()
+            kv[pages[b][p // 64], 1, :, p % 64] = v[p].cuda()
+        ks.append(k.float()), vs.append(v.float()), qs.append(q)
+    fb = FakeBatch(q_lens, starts, pages).sb
+    q_all = dev(torch.cat(qs))
+    ref = []
+    for b in range(len(q_lens)):
+        qq = torch.zeros(totals[b], heads, hd)
+        qq[starts[b]:] = qs[b].float()
+        ref.append(P.causal_attention(qq, ks[b], vs[b])[starts[b]:])
+    ref = torch.cat(ref)
+    got = {kind: ops.attention_prompt(q_all, kv, fb, 1 / math.sqrt(hd), kind=kind).float().cpu() for kind in ("tc", "mma", "plain")}
+    ops.check_status()
+    for kind, out in got.items():
+        assert torch.isfinite(out).all(), kind
+        assert (out - ref).abs().max() < tol(torch.bfloat16, 2), kind
+    assert (got["tc"] - got["mma"]).abs().max() < tol(torch.bfloat16, 2)
 
 
 @pytest.mark.parametrize("m, n, k", [(1, 72, 64), (7, 333, 100), (130, 192, 96), (64, 1000, 72)])

@@ -1,0 +1,472 @@
+// Causal attention of a step's new tokens over the paged cache on the 5th-
+// generation tensor cores (tcgen05), bfloat16, head sizes 64 and 128.
+//
+// A block takes one query head and 128 consecutive new tokens of one sequence
+// (two of the step's 64-row work items) and walks over the keys in blocks of 128
+// (two cache pages):
+//   * a producer thread fetches the query rows once and the key and value pages
+//     through a ring of six tiles (TMA, 64 x 64 boxes, 128-byte swizzle); a key
+//     tile is free again as soon as its scores are computed;
+//   * an issuing thread computes S = Q K^T into one of two 128-column buffers
+//     of tensor memory and accumulates O += P V (the values are the MN-major
+//     operand: their rows are keys);
+//   * two groups of four warps take the key blocks in turn (even blocks, odd
+//     blocks), each with a score buffer, an accumulator O, a maximum and a sum of
+//     its own, so that one group's exponentials overlap the other's waits; a
+//     thread owns one query row: it reads S from tensor memory, scales, masks
+//     (a key is visible up to the token's own position), and writes P as pairs
+//     of bfloat16 back into tensor memory over the scores it came from, where
+//     the second product takes it from.  At the end the two groups' results
+//     are merged like the splits of a decode step.
+// O and the sum are scaled by a maximum that follows the true running maximum
+// lazily: only when a block's maximum exceeds it by more than 8 (in units of
+// log2 e) is O rescaled in tensor memory, so that after the first blocks of a row
+// the rescaling is rare; probabilities stay below 2^8, which bfloat16 and
+// float32 hold without loss of relative precision.
+// Value rows beyond the cached length are zeroed in shared memory before they
+// are multiplied (their weight is zero, but the row may hold anything).
+// Every wait is bounded and reports through the status word.
+// Formulas: wick src/model.rs:520-553.  The plain forms of this computation are
+// attn_prompt_mma_kernel (attn_prompt_mma.cu) and attn_prompt_kernel (attn.cu).
+#include <cuda.h>
+
+#include <type_traits>
+
+#include "common.cuh"
+#include "sm100.cuh"
+#include "tcgen05.cuh"
+
+#ifndef WICK_HD
+#error "compile with -DWICK_HD=<head_dim>"
+#endif
+
+namespace wick {
+namespace prompttc {
+
+constexpr bool SUPPORTED = WICK_HD == 64 || WICK_HD == 128;
+constexpr int HD = SUPPORTED ? WICK_HD : 64;           // other head sizes: the entry point refuses, the kernel is never launched
+constexpr int kPage = 64;
+constexpr int BQ = 128;                                // query rows of a block
+constexpr int BK = 128;                                // keys of an inner step (two pages)
+constexpr int PANELS = HD / 64;                        // 64-column panels of a head row
+constexpr int PANEL_BYTES = 128 * 128;                 // 128 rows of 128 bytes
+constexpr int TILE_BYTES = PANELS * PANEL_BYTES;       // Q, or one block of keys or of values
+constexpr int NSLOT = 6;                               // key / value tiles in flight (3 blocks)
+constexpr int SMEM_BYTES = TILE_BYTES + NSLOT * TILE_BYTES + 1024;
+constexpr int THREADS = 320;                           // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-5 and 6-9: softmax groups
+constexpr uint32_t TMEM_COLS = 512;                    // S0 | S1 | O0 | O1; P (bfloat16 pairs) takes the place of the
+constexpr uint32_t COL_S = 0, COL_O = 256;             // first 64 columns of the S buffer it was computed from
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_ld32_nowait(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tc_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// The issuing thread is one thread: what it computes per instruction is what limits
+// the rate of small products.  A shared-memory descriptor is therefore kept as two
+// 32-bit halves: the high half is a constant, the low half (start address in 16-byte
+// units, leading offset) moves by one addition per instruction.
+__device__ __forceinline__ uint32_t desc_lo(uint32_t addr, uint32_t lbo_bytes) {
+    return ((addr & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+// stride offset 1024 bytes (8 rows of 128 bytes), descriptor version 1 (bit 46), 128-byte swizzle (bits 61-63)
+constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);
+
+// D (tensor memory) (+)= A (shared memory) * B (shared memory)
+template <int ACC>
+__device__ __forceinline__ void mma_ss(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+        "mov.b64 da, {%1, %3};\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+        ::"r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(DESC_HI), "r"(idesc), "n"(ACC)
+        : "memory");
+}
+// D (tensor memory) (+)= A (tensor memory: 128 lanes x 8 columns of bfloat16 pairs) * B (shared memory)
+template <int ACC>
+__device__ __forceinline__ void mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "r"(b_lo), "r"(DESC_HI), "r"(idesc), "n"(ACC)
+        : "memory");
+}
+template <int I, int N, typename F>
+__device__ __forceinline__ void static_for(F&& f) {
+    if constexpr (I < N) {
+        f(std::integral_constant<int, I>{});
+        static_for<I + 1, N>(f);
+    }
+}
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Descriptors.  A k-major operand (Q, K): rows of 128 bytes, eight-row groups 1024
+// bytes apart, the leading offset unused (1).  The MN-major operand (V): rows are
+// keys, a row holds 64 consecutive dims in 128 bytes, eight rows make a 1024-byte
+// group, and the next 64 dims lie one panel (the leading offset) further.
+
+__global__ void __launch_bounds__(THREADS, 1)
+attn_prompt_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map,
+                      bf16* __restrict__ out, const int* __restrict__ tile_seq, const int* __restrict__ tile_q0,
+                      const int* __restrict__ cu_seqlens, const int* __restrict__ start_arr,
+                      const int* __restrict__ page_table, int table_width, int n_tiles, int n_heads, int n_kv,
+                      float scale, int* status) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint64_t q_full, full[NSLOT], empty[NSLOT];
+    __shared__ uint64_t s_full[2], p_full[2], pv_done[2], fin_bar[4];
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+
+    pdl_trigger();
+    // longest first: the last work items of a sequence see the most keys
+    const int tile = n_tiles - 1 - (int)blockIdx.x;
+    const int q0 = tile_q0[tile];                                  // written by the host before the step: no kernel produces it
+    if (q0 % BQ != 0) return;                                      // the odd 64-row item belongs to its even neighbour's block
+    const int b = tile_seq[tile];
+    const int head = blockIdx.y, kvh = head / (n_heads / n_kv);
+    const int tok0 = cu_seqlens[b], q_len = cu_seqlens[b + 1] - tok0, start = start_arr[b];
+    const int kv_len = start + q_len;
+    const int rows = min(BQ, q_len - q0);
+    const int last_key = min(start + q0 + BQ - 1, kv_len - 1);     // the last position any row of the block may see
+    const int n_blk = last_key / BK + 1;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint8_t* base = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* q_s = base;
+    uint8_t* kv_s = q_s + TILE_BYTES;                              // NSLOT tiles: keys and values of the blocks in flight
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(&q_full, 1);
+        for (int s = 0; s < NSLOT; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&s_full[i], 1);
+            mbar_init(&p_full[i], 4);                              // one arrival per warp of the group
+            mbar_init(&pv_done[i], 1);
+        }
+        for (int i = 0; i < 4; ++i) mbar_init(&fin_bar[i], 2);     // the two warps that share 32 rows
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    pdl_wait();                                                    // q and the cache come from the kernel before this one
+
+    if (warp == 0) {
+        // ---------------- producer ----------------
+        // Items in order K_0, V_0, K_1, V_1, ...; item i lives in slot i % NSLOT.
+        if (lane == 0) {
+            mbar_expect_tx(&q_full, TILE_BYTES);
+            for (int pn = 0; pn < PANELS; ++pn) tma_load_2d(&q_map, &q_full, q_s + pn * PANEL_BYTES, head * HD + pn * 64, tok0 + q0);
+            for (int i = 0; i < 2 * n_blk; ++i) {
+                const int slot = i % NSLOT, j = i >> 1, is_v = i & 1;
+                if (!mbar_wait(&empty[slot], ((i / NSLOT) & 1) ^ 1, &abort_flag, status, 7)) break;
+                mbar_expect_tx(&full[slot], TILE_BYTES);
+                for (int w = 0; w < 2; ++w) {
+                    const int idx = 2 * j + w;
+                    const int page = idx < table_width ? page_table[(int64_t)b * table_width + idx] : 0;
+                    for (int pn = 0; pn < PANELS; ++pn)
+                        tma_load_2d(&kv_map, &full[slot], kv_s + slot * TILE_BYTES + pn * PANEL_BYTES + w * (kPage * 128), pn * 64,
+                                    ((page * 2 + is_v) * n_kv + kvh) * kPage);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        // Block j belongs to group j & 1: scores in S[j & 1], accumulator O[j & 1].
+        // (Measured on this part: the tensor core takes an instruction of this kind every
+        // ~93 clocks at best, whatever its width up to N = 128; 16 of them make a block.)
+        if (lane == 0) {
+            // kind::f16, bfloat16 operands, float32 accumulator, M = 128
+            const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BK >> 3) << 17) | ((uint32_t)(BQ >> 4) << 24);
+            const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((uint32_t)(HD >> 3) << 17) | ((uint32_t)(BQ >> 4) << 24);
+            const uint32_t q_lo = desc_lo(smem_u32(q_s), 16);
+            const uint32_t k_lo0 = desc_lo(smem_u32(kv_s), 16), v_lo0 = desc_lo(smem_u32(kv_s), PANEL_BYTES);
+            auto issue_s = [&](int j) -> bool {
+                const int i = 2 * j, slot = i % NSLOT, g = j & 1;
+                if (!mbar_wait(&full[slot], (i / NSLOT) & 1, &abort_flag, status, 7)) return false;
+                tc_fence_after();
+                const uint32_t k_lo = k_lo0 + slot * (TILE_BYTES >> 4), d = tmem + COL_S + g * BK;
+                static_for<0, HD / 16>([&](auto ks) {
+                    constexpr uint32_t off = (((int)ks >> 2) * PANEL_BYTES + ((int)ks & 3) * 32) >> 4;
+                    mma_ss<((int)ks > 0)>(d, q_lo + off, k_lo + off, idesc_s);
+                });
+                tc_commit(&s_full[g]);
+                tc_commit(&empty[slot]);                                     // the keys are read
+                return true;
+            };
+            bool ok = mbar_wait(&q_full, 0, &abort_flag, status, 7);
+            ok = ok && issue_s(0);
+            if (n_blk > 1) ok = ok && issue_s(1);
+            for (int j = 0; j < n_blk && ok; ++j) {
+                const int i = 2 * j + 1, slot = i % NSLOT, g = j & 1, u = j >> 1;
+                ok = ok && mbar_wait(&p_full[g], u & 1, &abort_flag, status, 7);
+                ok = ok && mbar_wait(&full[slot], (i / NSLOT) & 1, &abort_flag, status, 7);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t v_lo = v_lo0 + slot * (TILE_BYTES >> 4), d = tmem + COL_O + g * HD, pa = tmem + COL_S + g * BK;
+                if (u > 0) mma_ts<1>(d, pa, v_lo, idesc_o);
+                else mma_ts<0>(d, pa, v_lo, idesc_o);
+                static_for<1, BK / 16>([&](auto ks) { mma_ts<1>(d, pa + (int)ks * 8, v_lo + (int)ks * (2048 >> 4), idesc_o); });
+                tc_commit(&pv_done[g]);
+                tc_commit(&empty[slot]);                                     // the values are read
+                if (j + 2 < n_blk) {
+                    // the group's next scores go where this block's P lies: only when it has been read
+                    ok = mbar_wait(&pv_done[g], u & 1, &abort_flag, status, 7) && issue_s(j + 2);
+                }
+            }
+        }
+    } else {
+        // ---------------- softmax: two groups, one query row per thread ----------------
+        const int g = (warp - 2) >> 2;                              // warps 2-5: even blocks, warps 6-9: odd blocks
+        const int quad = warp & 3;                                  // the 32 lanes of tensor memory this warp may touch
+        const int r = quad * 32 + lane;
+        const int q_pos = start + q0 + r;
+        const int limit = min(q_pos, kv_len - 1);                   // last visible key position
+        const float sl2 = scale * 1.4426950408889634f;
+        const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16);
+        const uint32_t s_addr = lane_base + COL_S + g * BK, o_addr = lane_base + COL_O + g * HD;
+        float m = -INFINITY, l = 0.f;                               // the group's scaling maximum (units of log2 e) and sum
+        bool ok = true;
+        for (int j = g; j < n_blk; j += 2) {
+            const int u = j >> 1, v_item = 2 * j + 1, v_slot = v_item % NSLOT;
+            ok = __all_sync(0xffffffffu, mbar_wait(&s_full[g], u & 1, &abort_flag, status, 7));
+            if (!ok) break;
+            tc_fence_after();
+            const int key0 = j * BK;
+            const bool masked = key0 + BK - 1 > limit;
+            // pass 1: the block's maximum of the row
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int h = 0; h < BK; h += 64) {
+                float s[64];
+                __syncwarp();
+                tc_ld32_nowait(s_addr + h, reinterpret_cast<uint32_t*>(s));
+                tc_ld32_nowait(s_addr + h + 32, reinterpret_cast<uint32_t*>(s + 32));
+                tc_ld_wait();
+                if (masked) {
+#pragma unroll
+                    for (int i = 0; i < 64; ++i)
+                        if (key0 + h + i > limit) s[i] = -INFINITY;
+                }
+#pragma unroll
+                for (int i = 0; i < 64; i += 4) {
+                    mx4[0] = fmaxf(mx4[0], s[i]);
+                    mx4[1] = fmaxf(mx4[1], s[i + 1]);
+                    mx4[2] = fmaxf(mx4[2], s[i + 2]);
+                    mx4[3] = fmaxf(mx4[3], s[i + 3]);
+                }
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2;
+            const bool grow = mx > m + 8.0f;
+            float alpha = 1.0f;
+            if (grow) {
+                alpha = ex2(m - mx);                                // 0 for the first keys a row sees
+                m = mx;
+            }
+            const float neg_m = m == -INFINITY ? 0.f : -m;          // a row that sees no key yet
+            if (u > 0) {
+                // the group's last product is in O
+                ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[g], (u - 1) & 1, &abort_flag, status, 7));
+                if (!ok) break;
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, grow)) {
+#pragma unroll
+                    for (int c = 0; c < HD; c += 32) {
+                        uint32_t raw[32];
+                        tc_ld32_nowait(o_addr + c, raw);
+                        tc_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) raw[i] = __float_as_uint(__uint_as_float(raw[i]) * alpha);
+                        tc_st32(o_addr + c, raw);
+                    }
+                    tc_st_wait();
+                }
+            }
+            // pass 2: probabilities, their sum, and P over the first 64 columns of the scores
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int h = 0; h < BK; h += 64) {
+                float s[64];
+                __syncwarp();
+                tc_ld32_nowait(s_addr + h, reinterpret_cast<uint32_t*>(s));
+                tc_ld32_nowait(s_addr + h + 32, reinterpret_cast<uint32_t*>(s + 32));
+                tc_ld_wait();
+                if (masked) {
+#pragma unroll
+                    for (int i = 0; i < 64; ++i)
+                        if (key0 + h + i > limit) s[i] = -INFINITY;
+                }
+                uint32_t packed[32];
+#pragma unroll
+                for (int i = 0; i < 64; i += 2) {
+                    const float p0 = ex2(fmaf(s[i], sl2, neg_m)), p1 = ex2(fmaf(s[i + 1], sl2, neg_m));
+                    sum4[(i >> 1) & 3] += p0 + p1;
+                    __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);     // key 2k in the low half, key 2k + 1 in the high half
+                    packed[i >> 1] = *reinterpret_cast<uint32_t*>(&hh);
+                }
+                __syncwarp();
+                tc_st32(s_addr + (h >> 1), packed);                      // keys h .. h + 63 -> columns h / 2 .. h / 2 + 31
+            }
+            tc_st_wait();
+            l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+            // value rows that hold no token yet are made zero before they are multiplied
+            const int valid = kv_len - key0;
+            if (valid < BK) {
+                ok = __all_sync(0xffffffffu, mbar_wait(&full[v_slot], (v_item / NSLOT) & 1, &abort_flag, status, 7));
+                if (!ok) break;
+                const int first = max(valid, 0);
+                for (int i = r; i < (BK - first) * (HD / 8); i += BQ) {
+                    const int row = first + i / (HD / 8), chunk = i % (HD / 8);
+                    *reinterpret_cast<uint4*>(kv_s + v_slot * TILE_BYTES + (chunk >> 3) * PANEL_BYTES + row * 128 +
+                                              (((chunk & 7) ^ (row & 7)) << 4)) = make_uint4(0, 0, 0, 0);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the zeros before the tensor core reads them
+            }
+            tc_fence_before();                                               // P and the rescaled O before it multiplies and accumulates
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&p_full[g]);
+        }
+        // the group's last product
+        const int mine = (n_blk - g + 1) / 2;                       // blocks this group has handled
+        if (ok && mine > 0) ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[g], (mine - 1) & 1, &abort_flag, status, 7));
+        // (a group without a block still waits until the only scores are computed: the query tile is free then.
+        //  Otherwise the group's last product was issued after every score product, and has completed.)
+        if (ok && mine == 0) ok = __all_sync(0xffffffffu, mbar_wait(&s_full[0], 0, &abort_flag, status, 7));
+        tc_fence_after();
+        // Merge of the two groups: each tells the other its maximum and sum (through the
+        // query tile's shared memory, which no product reads any more), then group 0
+        // stores the first half of the row's dims and group 1 the second.
+        float* ml_x = reinterpret_cast<float*>(q_s);                // [group][m, l][row]
+        if (ok) {
+            ml_x[(g * 2 + 0) * BQ + r] = m;
+            ml_x[(g * 2 + 1) * BQ + r] = l;
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&fin_bar[quad]);
+            ok = __all_sync(0xffffffffu, mbar_wait(&fin_bar[quad], 0, &abort_flag, status, 7));
+            tc_fence_after();
+        }
+        if (ok) {
+            const float m0 = ml_x[0 * BQ + r], l0 = ml_x[1 * BQ + r], m1 = ml_x[2 * BQ + r], l1 = ml_x[3 * BQ + r];
+            const float mm = fmaxf(m0, m1);
+            const float w0 = m0 == -INFINITY ? 0.f : ex2(m0 - mm), w1 = m1 == -INFINITY ? 0.f : ex2(m1 - mm);
+            const float l_row = w0 * l0 + w1 * l1;
+            const bool store = r < rows && l_row > 0.f;
+            const float inv = store ? 1.0f / l_row : 0.f;
+            const bool two = n_blk > 1;                             // with one block the second accumulator was never written
+            constexpr int OW = HD / 2;
+            bf16* dst = out + ((int64_t)(tok0 + q0 + r) * n_heads + head) * HD + g * OW;
+#pragma unroll
+            for (int c = 0; c < OW; c += 32) {
+                // every lane takes part in the loads from tensor memory; only rows that exist are stored
+                uint32_t a[32], bb[32];
+                tc_ld32_nowait(lane_base + COL_O + g * OW + c, a);
+                if (two) tc_ld32_nowait(lane_base + COL_O + HD + g * OW + c, bb);
+                tc_ld_wait();
+                if (store) {
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint4 w;
+                        __nv_bfloat162* hh = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int e = 8 * q4 + 2 * i;
+                            float x0 = __uint_as_float(a[e]) * w0, x1 = __uint_as_float(a[e + 1]) * w0;
+                            if (two) {
+                                x0 = fmaf(__uint_as_float(bb[e]), w1, x0);
+                                x1 = fmaf(__uint_as_float(bb[e + 1]), w1, x1);
+                            }
+                            hh[i] = __floats2bfloat162_rn(x0 * inv, x1 * inv);
+                        }
+                        *reinterpret_cast<uint4*>(dst + c + 8 * q4) = w;
+                    }
+                }
+                __syncwarp();
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (abort_flag) {
+        const uint64_t t0 = global_ns();
+        while (global_ns() - t0 < 2000000ull) __nanosleep(1000);   // copies in flight land before the block leaves
+        __syncthreads();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS));
+    }
+}
+
+}  // namespace prompttc
+}  // namespace wick
+
+using namespace wick;
+
+WICK_API int wick_attn_prompt_tc_supported() { return prompttc::SUPPORTED ? 1 : 0; }
+
+// q, out: bfloat16 [n_tokens, n_heads, HD]; kv: one schedule entry's cache, bfloat16
+// [kv_pages, 2, n_kv, 64, HD] (it already holds the new tokens' keys and values);
+// tile_seq / tile_q0: the step's 64-row work items in sequence order; status: device
+// int (code 7 if a block gave up waiting).
+WICK_API int wick_attn_prompt_tc_bf16(const void* q, long long n_tokens, const void* kv, long long kv_pages, void* out,
+                                      const int* tile_seq, const int* tile_q0, int n_tiles, const int* cu_seqlens,
+                                      const int* start, const int* page_table, int table_width, int n_heads, int n_kv,
+                                      float scale, int* status, void* s) {
+    using namespace prompttc;
+    WICK_REQUIRE(SUPPORTED, "attention (tcgen05): head_dim %d is not 64 or 128", (int)WICK_HD);
+    WICK_REQUIRE(n_heads > 0 && n_kv > 0 && n_heads % n_kv == 0, "attention: %d heads over %d kv heads", n_heads, n_kv);
+    WICK_REQUIRE(n_heads <= 65535, "attention: %d heads is beyond the grid limit", n_heads);
+    if (n_tiles == 0) return 0;
+    CUtensorMap q_map, kv_map;
+    if (int e = make_bf16_map(&q_map, q, n_tokens, (long long)n_heads * HD, BQ, "attention (tcgen05)")) return e;
+    if (int e = make_bf16_map(&kv_map, kv, kv_pages * 2 * n_kv * kPage, HD, kPage, "attention (tcgen05)")) return e;
+    static bool raised = false;
+    if (!raised) {
+        WICK_CUDA(cudaFuncSetAttribute(attn_prompt_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+        raised = true;
+    }
+    WICK_CUDA(launch(attn_prompt_tc_kernel, dim3(n_tiles, n_heads), dim3(THREADS), (size_t)SMEM_BYTES, (cudaStream_t)s, q_map,
+                     kv_map, (bf16*)out, tile_seq, tile_q0, cu_seqlens, start, page_table, table_width, n_tiles, n_heads,
+                     n_kv, scale, status));
+    return check_launch("attn_prompt_tc");
+}

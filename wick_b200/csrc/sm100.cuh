@@ -34,8 +34,8 @@ __device__ __forceinline__ uint64_t global_ns() {
 }
 // Bounded wait.  Returns false (and raises the block's abort flag) after ~1 s.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+    if (mbar_try_wait(bar, parity)) return true;         // the common case costs one instruction
     if (*abort_flag) return false;
-    if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = global_ns();
     for (uint32_t spin = 0;; ++spin) {
         if (mbar_try_wait(bar, parity)) return true;

@@ -85,7 +85,7 @@ def _simt() -> _Lib:
     return lib
 
 
-ATTN_SOURCES = ["attn.cu", "attn_decode.cu", "attn_decode_mma.cu", "attn_prompt_mma.cu"]
+ATTN_SOURCES = ["attn.cu", "attn_decode.cu", "attn_decode_mma.cu", "attn_prompt_mma.cu", "attn_prompt_tc.cu"]
 
 
 def _attn(head_dim: int) -> _Lib:
@@ -105,7 +105,7 @@ def _attn(head_dim: int) -> _Lib:
 _status: Optional[torch.Tensor] = None
 _STATUS_TEXT = {1: "gemm_tc: a free shared-memory stage", 2: "gemm_tc: a TMA copy", 3: "gemm_tc: the accumulator",
                 4: "attention decode: its bulk copies", 5: "gemm_tc: a free accumulator",
-                6: "attention decode (tensor cores): its TMA copies"}
+                6: "attention decode (tensor cores): its TMA copies", 7: "attention (tcgen05): a copy or an accumulator"}
 
 
 def status_tensor(device) -> torch.Tensor:
@@ -289,12 +289,20 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, *, gated
 
 
 # ---------------------------------------------------------------------------
+def attention_prompt_kind(head_dim: int, dtype: torch.dtype, plain: bool = False) -> str:
+    """Which prompt kernel runs: ``tc`` (tcgen05: bfloat16, head sizes 64 and 128),
+    ``mma`` (mma.sync: bfloat16, other head sizes up to 128) or ``plain`` (CUDA
+    cores: float32, larger heads, and the twin the others are checked against)."""
+    if plain or dtype != torch.bfloat16 or head_dim > 128:
+        return "plain"
+    return "tc" if head_dim in (64, 128) else "mma"
+
+
 def attention_prompt(q: torch.Tensor, kv: torch.Tensor, batch, scale: float,
-                     out: Optional[torch.Tensor] = None, plain: bool = False) -> torch.Tensor:
+                     out: Optional[torch.Tensor] = None, plain: bool = False, kind: Optional[str] = None) -> torch.Tensor:
     """Causal attention of the step's new tokens over the cache (which already
     holds their keys and values).  q: [n, heads, d]; kv: [pages, 2, kv_heads, 64, d].
-    bfloat16 with a head size up to 128 runs on the tensor cores unless ``plain``
-    asks for the CUDA-core form (which is also the float32 kernel)."""
+    ``kind`` (see :func:`attention_prompt_kind`) picks a kernel by hand."""
     _cuda("q", q)
     n, n_heads, hd = q.shape
     _cuda("kv", kv, q.dtype)
@@ -305,8 +313,15 @@ def attention_prompt(q: torch.Tensor, kv: torch.Tensor, batch, scale: float,
     if out is None:
         out = torch.empty_like(q)
     _cuda("out", out, q.dtype, q.shape)
-    fast = q.dtype == torch.bfloat16 and hd <= 128 and not plain
-    _attn(hd).call("wick_attn_prompt_mma_bf16" if fast else f"wick_attn_prompt_{_dt(q)}", "pppppipppiiifp",
+    kind = kind or attention_prompt_kind(hd, q.dtype, plain)
+    _need(kind == "plain" or q.dtype == torch.bfloat16, "the tensor-core attention kernels take bfloat16")
+    if kind == "tc":
+        _attn(hd).call("wick_attn_prompt_tc_bf16", "plplpppipppiiifpp", _p(q), n, _p(kv), kv.shape[0], _p(out),
+                       _p(batch.tile_seq), _p(batch.tile_q0), batch.n_tiles, _p(batch.cu_seqlens), _p(batch.start),
+                       _p(batch.page_table), batch.table_width, n_heads, n_kv, float(scale),
+                       _p(status_tensor(q.device)), _stream())
+        return out
+    _attn(hd).call("wick_attn_prompt_mma_bf16" if kind == "mma" else f"wick_attn_prompt_{_dt(q)}", "pppppipppiiifp",
                    _p(q), _p(kv), _p(out), _p(batch.tile_seq),
                    _p(batch.tile_q0), batch.n_tiles, _p(batch.cu_seqlens), _p(batch.start), _p(batch.page_table),
                    batch.table_width, n_heads, n_kv, float(scale), _stream())
