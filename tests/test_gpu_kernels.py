@@ -206,6 +206,57 @@ def test_attention_finds_one_far_key_among_hundreds(ops, dtype, hd):
         assert (outp[4] - want).abs().max() < 1e-2, f"prompt kernel missed key {far}"
 
 
+@pytest.mark.parametrize("heads, kv_heads, hd, lens", [(8, 2, 128, (1, 130, 700, 64)), (4, 4, 64, (129, 5)),
+                                                        (16, 2, 128, (300,)), (6, 2, 64, (2000, 65, 128, 127, 1, 1025))])
+def test_decode_attention_in_one_kernel(ops, heads, kv_heads, hd, lens):
+    """The fused decode kernel (norm, rotation, cache append, attention, merge) against
+    the three kernels it replaces, on the same float32 partial sums: same output, and
+    the same key and value rows in the cache.  Lengths around the 128-position chunk
+    and the 64-position page; scrambled pages; NaN wherever the cache holds no token."""
+    assert ops.attention_decode_fused_supported(len(lens), heads, kv_heads, hd, torch.bfloat16)
+    assert not ops.attention_decode_fused_supported(200, heads, kv_heads, hd, torch.bfloat16)
+    torch.manual_seed(hd + heads + len(lens))
+    B = len(lens)
+    n_pages = sum((t + 63) // 64 for t in lens) + 1
+    perm = (torch.randperm(n_pages - 1) + 1).tolist()
+    pages, o = [], 0
+    for t in lens:
+        n = (t + 63) // 64
+        pages.append(perm[o:o + n])
+        o += n
+    kv_a = _paged(n_pages, kv_heads, hd, torch.bfloat16)
+    for b, t in enumerate(lens):                                # the positions before the new token
+        for p in range(t - 1):
+            kv_a[pages[b][p // 64], :, :, p % 64] = torch.randn(2, kv_heads, hd).bfloat16().cuda()
+    kv_b = kv_a.clone()
+    fd = FakeBatch([1] * B, [t - 1 for t in lens], pages).sb
+    width = (heads + 2 * kv_heads) * hd
+    parts = dev(torch.randn(3, B, width) * 0.6)
+    qw, kw = dev(1 + 0.1 * torch.randn(hd)), dev(1 + 0.1 * torch.randn(hd))
+    cos, sin = ops.rope_table(fd.positions, dev(P.rope_inv_freq(10000.0, hd)))
+    scale = 1 / math.sqrt(hd)
+    q = ops.qk_norm_rope_append(parts, heads, kv_heads, hd, q_weight=qw, k_weight=kw, eps=1e-6, cos=cos, sin=sin, kv=kv_a,
+                                page_table=fd.page_table, seq_of_token=fd.seq_of_token, positions=fd.positions,
+                                dtype=torch.bfloat16)
+    scratch = torch.empty(ops.attention_decode_scratch_floats(B, heads, hd, max(lens), torch.bfloat16), device="cuda")
+    want = ops.attention_decode(q, kv_a, fd, scale, scratch).float()
+    got = ops.attention_decode_fused(parts, heads, kv_heads, hd, q_weight=qw, k_weight=kw, eps=1e-6, cos=cos, sin=sin,
+                                     kv=kv_b, batch=fd, scale=scale).float()
+    ops.check_status()
+    assert torch.isfinite(got).all()
+    assert (got - want).abs().max() < tol(torch.bfloat16, 1)
+    for b, t in enumerate(lens):                                # the new token's rows, and nothing else, were written
+        page, row = pages[b][(t - 1) // 64], (t - 1) % 64
+        assert torch.equal(kv_b[page, :, :, row], kv_a[page, :, :, row])
+    assert torch.equal(torch.nan_to_num(kv_b.float(), nan=-7.0), torch.nan_to_num(kv_a.float(), nan=-7.0))
+    # reading another entry's cache: nothing is written, the cache's own row is used
+    kv_c = kv_a.clone()
+    again = ops.attention_decode_fused(parts, heads, kv_heads, hd, q_weight=qw, k_weight=kw, eps=1e-6, cos=cos, sin=sin,
+                                       kv=kv_c, batch=fd, scale=scale, write_kv=False).float()
+    assert torch.equal(torch.nan_to_num(kv_c.float(), nan=-7.0), torch.nan_to_num(kv_a.float(), nan=-7.0))
+    assert (again - want).abs().max() < tol(torch.bfloat16, 1)
+
+
 @pytest.mark.parametrize("heads, kv_heads, hd", [(4, 2, 128), (6, 3, 64), (3, 1, 128)])
 def test_prompt_attention_on_tcgen05(ops, heads, kv_heads, hd):
     """The tcgen05 prompt kernel against the plain parts and its two twins: several

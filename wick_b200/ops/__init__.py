@@ -9,6 +9,7 @@ any kind: without a CUDA device or without ``nvcc`` these functions raise.
 from __future__ import annotations
 
 import ctypes
+import os
 import math
 from typing import Dict, Optional, Tuple
 
@@ -85,7 +86,7 @@ def _simt() -> _Lib:
     return lib
 
 
-ATTN_SOURCES = ["attn.cu", "attn_decode.cu", "attn_decode_mma.cu", "attn_prompt_mma.cu", "attn_prompt_tc.cu"]
+ATTN_SOURCES = ["attn.cu", "attn_decode.cu", "attn_decode_mma.cu", "attn_decode_fused.cu", "attn_prompt_mma.cu", "attn_prompt_tc.cu"]
 
 
 def _attn(head_dim: int) -> _Lib:
@@ -105,7 +106,8 @@ def _attn(head_dim: int) -> _Lib:
 _status: Optional[torch.Tensor] = None
 _STATUS_TEXT = {1: "gemm_tc: a free shared-memory stage", 2: "gemm_tc: a TMA copy", 3: "gemm_tc: the accumulator",
                 4: "attention decode: its bulk copies", 5: "gemm_tc: a free accumulator",
-                6: "attention decode (tensor cores): its TMA copies", 7: "attention (tcgen05): a copy or an accumulator"}
+                6: "attention decode (tensor cores): its TMA copies", 7: "attention (tcgen05): a copy or an accumulator",
+                8: "attention decode (fused): its TMA copies"}
 
 
 def status_tensor(device) -> torch.Tensor:
@@ -395,6 +397,61 @@ def attention_decode(q: torch.Tensor, kv: torch.Tensor, batch, scale: float, scr
                        _p(scratch), scratch.numel(), _p(batch.kv_len), n, mk, _p(batch.page_table),
                        batch.table_width, n_heads, n_kv, float(scale), _p(status_tensor(q.device)), _stream(),
                        kernels=2)
+    return out
+
+
+_fused_ok: Dict[tuple, bool] = {}
+
+
+def attention_decode_fused_supported(n_seqs: int, n_heads: int, n_kv: int, head_dim: int, dtype: torch.dtype) -> bool:
+    """Whether the one-kernel decode attention (q/k norm, rotation, cache append,
+    attention and merge in one launch) takes this problem: bfloat16, head size 64
+    or 128, at most 8 query heads per kv head, and few enough (sequence, kv head)
+    pairs for all of its blocks to run at once."""
+    if dtype != torch.bfloat16 or head_dim not in (64, 128) or os.environ.get("WICK_B200_NO_FUSED_DECODE"):
+        return False
+    key = (n_seqs, n_heads, n_kv, head_dim)
+    v = _fused_ok.get(key)
+    if v is None:
+        f = _attn(head_dim)._lib.wick_attn_decode_fused_supported
+        f.restype = ctypes.c_int
+        f.argtypes = [ctypes.c_int] * 3
+        v = _fused_ok[key] = bool(f(n_seqs, n_heads, n_kv))
+    return v
+
+
+def attention_decode_fused(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, *,
+                           q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                           cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], kv: torch.Tensor, batch,
+                           scale: float, write_kv: bool = True, max_kv_len: Optional[int] = None,
+                           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One new token per sequence, from the projection's float32 partial sums
+    ``qkv`` [splits, n, (n_heads + 2 n_kv) head_dim] to the attention output
+    [n, n_heads, head_dim] (bfloat16) in one launch: per-head norm of q and k,
+    rotation, the new key and value into the cache (unless ``write_kv`` is False),
+    attention over the cache, merge."""
+    _cuda("qkv", qkv, torch.float32)
+    width = (n_heads + 2 * n_kv) * head_dim
+    n = batch.n_seqs
+    _need(qkv.dim() == 3 and tuple(qkv.shape[1:]) == (n, width), f"qkv must be [splits, {n}, {width}], is {tuple(qkv.shape)}")
+    for nm, w in (("q_weight", q_weight), ("k_weight", k_weight)):
+        if w is not None:
+            _cuda(nm, w, torch.float32, (head_dim,))
+    _need((q_weight is None) == (k_weight is None), "q and k norm weights come together")
+    if cos is not None:
+        _cuda("cos", cos, torch.float32, (n, head_dim // 2))
+        _cuda("sin", sin, torch.float32, (n, head_dim // 2))
+    _cuda("kv", kv, torch.bfloat16)
+    _need(kv.dim() == 5 and tuple(kv.shape[1:]) == (2, n_kv, PAGE, head_dim),
+          f"kv must be [pages, 2, {n_kv}, {PAGE}, {head_dim}], is {tuple(kv.shape)}")
+    if out is None:
+        out = torch.empty((n, n_heads, head_dim), dtype=torch.bfloat16, device=qkv.device)
+    _cuda("out", out, torch.bfloat16, (n, n_heads, head_dim))
+    mk = batch.max_kv_len if max_kv_len is None else max_kv_len
+    _attn(head_dim).call("wick_attn_decode_fused_bf16", "piippfppplppipiiifipp", _p(qkv), qkv.shape[0], n, _p(q_weight),
+                         _p(k_weight), float(eps), _p(cos), _p(sin), _p(kv), kv.shape[0], _p(out), _p(batch.kv_len), mk,
+                         _p(batch.page_table), batch.table_width, n_heads, n_kv, float(scale), 1 if write_kv else 0,
+                         _p(status_tensor(qkv.device)), _stream())
     return out
 
 

@@ -161,6 +161,15 @@ class GQAttention(Mixer):
             cos = sin = None
             if inv_freq is not None:
                 cos, sin = self.position.tables(batch)
+            if batch.is_decode and qkv.shape[0] <= 8 and ops.attention_decode_fused_supported(batch.n_seqs, self.heads, self.kv_heads,
+                                                                        self.head_dim, self.ctx.dtype):
+                att = ops.attention_decode_fused(
+                    qkv, self.heads, self.kv_heads, self.head_dim,
+                    q_weight=self.q_norm.weight if self.q_norm else None,
+                    k_weight=self.k_norm.weight if self.k_norm else None,
+                    eps=self.q_norm.eps if self.q_norm else 0.0, cos=cos, sin=sin, kv=cache.kv, batch=batch,
+                    scale=self.scale, write_kv=write_cache, max_kv_len=batch.kv_bound)
+                return self.o.forward_delta(att.view(batch.n_tokens, self.q_dim))
             q = ops.qk_norm_rope_append(
                 qkv, self.heads, self.kv_heads, self.head_dim,
                 q_weight=self.q_norm.weight if self.q_norm else None,
