@@ -166,6 +166,30 @@ def test_head_dim_64_prompt_then_long_decode_in_a_batch(dtype, graphs):
         eng.close_seq(s)
 
 
+@pytest.mark.parametrize("graphs", [False, True])
+def test_short_kernels_overlap_in_a_captured_step(graphs):
+    """Config E in bfloat16: kernels of a few microseconds each, launched back to
+    back from a captured step, each allowed to start before the one before it has
+    ended.  A kernel that read its input before waiting for its producer gave
+    logits that were off by half their range here (and nowhere else)."""
+    name = "E"
+    eng = make_engine(name, "bfloat16", use_graphs=graphs)
+    poison_all(eng)
+    lens = (290, 130)
+    seqs = [random_tokens(vocab_of(name), n + 40, 70 + n) for n in lens]
+    refs = [plain_logits(name, s) for s in seqs]
+    slots = [eng.open_seq() for _ in seqs]
+    got = eng.step(slots, [s[:n] for s, n in zip(seqs, lens)], [[n - 1] for n in lens]).clone()
+    for i, n in enumerate(lens):
+        assert_logits_close(got[i], refs[i][n - 1], "bfloat16", f"E prompt {i}")
+    for k in range(40):
+        got = eng.step(slots, [[s[n + k]] for s, n in zip(seqs, lens)]).clone()
+        for i, n in enumerate(lens):
+            assert_logits_close(got[i], refs[i][n + k], "bfloat16", f"E seq {i} decode {k}")
+    for s in slots:
+        eng.close_seq(s)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", NAMES)
 def test_first_tokens_of_a_sequence(name, dtype):

@@ -54,6 +54,8 @@ attn_decode_fast_kernel(const T* __restrict__ q, const T* __restrict__ kv, float
     constexpr int TS = S::TS, CPL = S::CPL, KPI = S::KPI;
     pdl_trigger();
     pdl_wait();
+    q = fresh(q);
+    kv = fresh(kv);
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int kv_len = kv_len_arr[b];
     const int key_begin = split * SPLIT;
@@ -234,6 +236,8 @@ __global__ void attn_decode_fast_merge_kernel(const float* __restrict__ part_o, 
     constexpr int SPLIT = Shape<T>::SPLIT;
     pdl_trigger();
     pdl_wait();
+    part_o = fresh(part_o);
+    part_ml = fresh(part_ml);
     const int head = blockIdx.x, b = blockIdx.y;
     const int n_splits = (kv_len_arr[b] + SPLIT - 1) / SPLIT;
     const int64_t row0 = ((int64_t)b * n_heads + head) * max_splits;

@@ -96,6 +96,15 @@ __device__ __forceinline__ void st_remote(float* p, uint32_t rank, float v) {
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(smem_u32(p)), "r"(rank));
     asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(a), "f"(v) : "memory");
 }
+// A load of something that a kernel still in flight when this one starts has written
+// (the projection's partial sums, the rotation tables): never through the read-only
+// path, and never moved above the wait for that kernel (which the compiler may do with
+// an ordinary load through a const __restrict__ pointer).
+__device__ __forceinline__ float ld_fresh(const float* p) {
+    float v;
+    asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+    return v;
+}
 // 2^(a - b) for maxima that may be -inf (nothing seen yet): then the weight is 0.
 __device__ __forceinline__ float weight(float a, float b) { return a == -INFINITY ? 0.f : exp2f(a - b); }
 
@@ -111,9 +120,9 @@ struct alignas(16) Shared {
 };
 
 __global__ void __launch_bounds__(THREADS, 1)
-attn_decode_fused_kernel(const __grid_constant__ CUtensorMap kv_map, const float* __restrict__ parts, int splits,
+attn_decode_fused_kernel(const __grid_constant__ CUtensorMap kv_map, const float* parts, int splits,
                          int64_t split_stride, const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
-                         const float* __restrict__ cos_t, const float* __restrict__ sin_t, bf16* __restrict__ kv,
+                         const float* cos_t, const float* sin_t, bf16* __restrict__ kv,
                          bf16* __restrict__ out, const int* __restrict__ kv_len_arr, const int* __restrict__ page_table,
                          int table_width, int n_heads, int n_kv, float scale, int write_kv, int* status) {
     extern __shared__ uint8_t smem_raw[];
@@ -194,7 +203,7 @@ attn_decode_fused_kernel(const __grid_constant__ CUtensorMap kv_map, const float
             for (int sp = 0; sp < MAX_SPLITS; ++sp)
 #pragma unroll
                 for (int e = 0; e < EPL; ++e)
-                    raw[sp][e] = (used && sp < splits) ? row[sp * split_stride + off + lane + 32 * e] : 0.f;
+                    raw[sp][e] = (used && sp < splits) ? ld_fresh(row + sp * split_stride + off + lane + 32 * e) : 0.f;
 #pragma unroll
             for (int e = 0; e < EPL; ++e) {
                 float x = raw[0][e];
@@ -228,7 +237,7 @@ attn_decode_fused_kernel(const __grid_constant__ CUtensorMap kv_map, const float
                     y = (y * sc) * w[i + half];
                 }
                 if (cos_t && !is_v) {
-                    const float c = cos_t[(int64_t)b * half + i], sn = sin_t[(int64_t)b * half + i];
+                    const float c = ld_fresh(cos_t + (int64_t)b * half + i), sn = ld_fresh(sin_t + (int64_t)b * half + i);
                     const float rx = x * c - y * sn, ry = y * c + x * sn;
                     x = rx;
                     y = ry;

@@ -347,6 +347,8 @@ __global__ void attn_decode_mma_merge_kernel(const float* __restrict__ part_o, c
                                              int max_splits) {
     pdl_trigger();
     pdl_wait();
+    part_o = fresh(part_o);
+    part_ml = fresh(part_ml);
     const int head = blockIdx.x, b = blockIdx.y;
     const int n_splits = (kv_len_arr[b] + SPLIT - 1) / SPLIT;
     const int64_t row0 = ((int64_t)b * n_heads + head) * max_splits;

@@ -79,6 +79,8 @@ attn_prompt_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv, 
     bf16* Vs = Ks + 2 * kPage * HD;                            // [2][64][HD]
     pdl_trigger();
     pdl_wait();
+    q = fresh(q);
+    kv = fresh(kv);
 
     const int tile = n_tiles - 1 - blockIdx.x;                 // long tiles (late rows of long prompts) first
     const int head = blockIdx.y;

@@ -138,6 +138,17 @@ inline int ceil_div(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }
 // come before pdl_wait.  Both are no-ops for a kernel launched the ordinary way.
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// A pointer to data that the kernel before this one produces, as the compiler must
+// see it after pdl_wait: a value that exists only from here on.  Without this, a
+// load through a const __restrict__ pointer counts as a load of constant data and
+// may be moved above the wait (it was, in a kernel whose wait came late: the loads
+// then returned what the buffer held before).  Use as: p = fresh(p); right after
+// pdl_wait().
+template <typename T>
+__device__ __forceinline__ T* fresh(T* p) {
+    asm volatile("" : "+l"(p));
+    return p;
+}
 
 inline bool pdl_enabled() {
     static int on = -1;

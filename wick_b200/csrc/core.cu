@@ -37,6 +37,8 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
     extern __shared__ float smem[];
     pdl_trigger();
     pdl_wait();
+    x = fresh(x);
+    delta = fresh(delta);
     float* row = smem;
     float* red = smem + width;
     const int i = blockIdx.x;
@@ -124,6 +126,10 @@ __global__ void qk_norm_rope_append_kernel(
     const int* __restrict__ seq_of_token, const int* __restrict__ positions, int write_kv) {
     pdl_trigger();
     pdl_wait();
+    qkv = fresh(qkv);
+    parts = fresh(parts);
+    cos_t = fresh(cos_t);
+    sin_t = fresh(sin_t);
     const int lane = threadIdx.x & 31;
     const int heads_total = n_heads + (write_kv ? 2 * n_kv : 0);
     const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);

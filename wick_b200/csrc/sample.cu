@@ -18,6 +18,7 @@ __global__ void __launch_bounds__(ST) argmax_kernel(const float* __restrict__ lo
     __shared__ int si[32];
     pdl_trigger();
     pdl_wait();
+    logits = fresh(logits);
     const float* x = logits + (int64_t)blockIdx.x * vocab;
     float best = -INFINITY;
     int idx = INT_MAX;
