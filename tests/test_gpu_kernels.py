@@ -463,6 +463,15 @@ def test_gemm_tensor_core_single_blocks_and_pairs(monkeypatch, t, n, k, gated):
         G.check_status()
         assert (got32.cpu() - ref).abs().max() < 2e-4 * max(1.0, ref.abs().max()), pair_min
         assert (got16.float().cpu() - ref).abs().max() < 1e-2 * max(1.0, ref.abs().max()), pair_min
+    if not gated:
+        # the epilogue that adds into a float32 residual: same numbers as product + addition
+        monkeypatch.setattr(G, "PAIR_MIN", 256)
+        res = torch.randn(t, n)
+        acc = dev(res.clone())
+        assert plan.forward_add(dev(x), acc)
+        G.check_status()
+        assert torch.equal(acc, dev(res) + plan.forward(dev(x), torch.float32))
+        assert not plan.forward_add(dev(x[:100]), dev(res[:100].clone())), "few tokens: the caller adds"
 
 
 def ops_gemm_simt(x, w, gated):

@@ -87,7 +87,7 @@ __device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
                  ::"r"(smem_u32(bar)), "h"(mask) : "memory");
 }
 
-template <int GATED, bool OUT_F32>
+template <int GATED, bool OUT_F32, bool ACC>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
     extern __shared__ uint8_t smem_raw[];
@@ -225,10 +225,17 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                         if (OUT_F32) {
                             float* o = (float*)p.out + off;
                             if (n_left >= 16 && (off & 3) == 0) {
+                                if (ACC) {                      // out += product: the residual stream takes the result directly
+                                    float4 r[4];
+#pragma unroll
+                                    for (int j = 0; j < 4; ++j) r[j] = *(const float4*)(o + 4 * j);
+#pragma unroll
+                                    for (int j = 0; j < 4; ++j) { v[4 * j] += r[j].x; v[4 * j + 1] += r[j].y; v[4 * j + 2] += r[j].z; v[4 * j + 3] += r[j].w; }
+                                }
 #pragma unroll
                                 for (int j = 0; j < 16; j += 4) *(float4*)(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
                             } else {
-                                for (int j = 0; j < 16 && j < n_left; ++j) o[j] = v[j];
+                                for (int j = 0; j < 16 && j < n_left; ++j) o[j] = ACC ? o[j] + v[j] : v[j];
                             }
                         } else {
                             __nv_bfloat16* o = (__nv_bfloat16*)p.out + off;
@@ -268,12 +275,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
 }
 
-template <int GATED, bool OUT_F32>
+template <int GATED, bool OUT_F32, bool ACC>
 static int launch_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, const Params& p, int blocks, size_t smem,
                        cudaStream_t stream) {
     static bool raised = false;
     if (!raised) {
-        WICK_CUDA(cudaFuncSetAttribute(gemm_tc2_kernel<GATED, OUT_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        WICK_CUDA(cudaFuncSetAttribute(gemm_tc2_kernel<GATED, OUT_F32, ACC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         raised = true;
     }
     cudaLaunchConfig_t cfg = {};
@@ -290,7 +297,7 @@ static int launch_pair(const CUtensorMap& map_a, const CUtensorMap& map_b, const
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 2 : 1;
-    WICK_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<GATED, OUT_F32>, map_a, map_b, p));
+    WICK_CUDA(cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<GATED, OUT_F32, ACC>, map_a, map_b, p));
     return check_launch("gemm_tc2");
 }
 
@@ -301,12 +308,14 @@ using namespace wick;
 
 // a: activations [a_rows, k] bf16; b: weights [b_total_rows, k] bf16; out[m * ldo + n], n < b_rows.
 // gated: b holds gate rows [0, b_rows) and up rows [pair_offset, pair_offset + b_rows); the
-// output is silu(a gate^T) * (a up^T).  status as in wick_gemm_tc.
+// output is silu(a gate^T) * (a up^T).  accumulate (plain float32 output only): out += the product
+// (every element by one thread: no atomics).  status as in wick_gemm_tc.
 WICK_API int wick_gemm_tc2(const void* a, int a_rows, const void* b, long long b_total_rows, int b_rows, int k, int gated,
-                           int pair_offset, int out_f32, void* out, long long ldo, int* status, void* stream) {
+                           int pair_offset, int out_f32, int accumulate, void* out, long long ldo, int* status, void* stream) {
     using namespace pair;
     WICK_REQUIRE(a_rows > 0 && b_rows > 0 && k > 0, "gemm_tc2: bad sizes");
     WICK_REQUIRE(gated == 0 || gated == 1, "gemm_tc2: bad options");
+    WICK_REQUIRE(!accumulate || (out_f32 && !gated), "gemm_tc2: accumulation goes with a plain float32 output");
     CUtensorMap map_a, map_b;
     if (int e = make_bf16_map(&map_a, a, a_rows, k, BM, "gemm_tc2")) return e;
     if (int e = make_bf16_map(&map_b, b, b_total_rows, k, BNH, "gemm_tc2")) return e;
@@ -320,8 +329,9 @@ WICK_API int wick_gemm_tc2(const void* a, int a_rows, const void* b, long long b
     p.total_tiles = (int)total;
     const int pairs = p.total_tiles < 74 ? p.total_tiles : 74;       // 148 SMs
     const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;
-    if (gated) return out_f32 ? launch_pair<1, true>(map_a, map_b, p, 2 * pairs, smem, (cudaStream_t)stream)
-                              : launch_pair<1, false>(map_a, map_b, p, 2 * pairs, smem, (cudaStream_t)stream);
-    return out_f32 ? launch_pair<0, true>(map_a, map_b, p, 2 * pairs, smem, (cudaStream_t)stream)
-                   : launch_pair<0, false>(map_a, map_b, p, 2 * pairs, smem, (cudaStream_t)stream);
+    if (gated) return out_f32 ? launch_pair<1, true, false>(map_a, map_b, p, 2 * pairs, smem, (cudaStream_t)stream)
+                              : launch_pair<1, false, false>(map_a, map_b, p, 2 * pairs, smem, (cudaStream_t)stream);
+    if (accumulate) return launch_pair<0, true, true>(map_a, map_b, p, 2 * pairs, smem, (cudaStream_t)stream);
+    return out_f32 ? launch_pair<0, true, false>(map_a, map_b, p, 2 * pairs, smem, (cudaStream_t)stream)
+                   : launch_pair<0, false, false>(map_a, map_b, p, 2 * pairs, smem, (cudaStream_t)stream);
 }

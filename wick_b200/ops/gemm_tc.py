@@ -61,8 +61,9 @@ def gemm_tc(a: torch.Tensor, a_rows: int, b: torch.Tensor, b_rows: int, *, bn: i
 
 
 def gemm_tc_pair(a: torch.Tensor, b: torch.Tensor, b_rows: int, *, out: torch.Tensor, ldo: int, gated: bool = False,
-                 pair_offset: int = 0) -> None:
-    """The kernel for pairs of thread blocks (see ``wick_gemm_tc2`` in gemm_tc2.cu): out[m, n] = a[m] . b[n]."""
+                 pair_offset: int = 0, accumulate: bool = False) -> None:
+    """The kernel for pairs of thread blocks (see ``wick_gemm_tc2`` in gemm_tc2.cu): out[m, n] = a[m] . b[n],
+    or out[m, n] += ... with ``accumulate`` (float32 output)."""
     for nm, t in (("a", a), ("b", b)):
         if not (t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous() and t.dim() == 2):
             raise KernelError(f"gemm_tc_pair: {nm} must be a contiguous 2-D bfloat16 CUDA tensor")
@@ -71,8 +72,9 @@ def gemm_tc_pair(a: torch.Tensor, b: torch.Tensor, b_rows: int, *, out: torch.Te
     if out.dtype not in (torch.float32, torch.bfloat16) or not out.is_contiguous():
         raise KernelError("gemm_tc_pair: out must be contiguous float32 or bfloat16")
     st = status_tensor(a.device)
-    _lib().call("wick_gemm_tc2", "pipliiiiiplpp", _p(a), a.shape[0], _p(b), b.shape[0], b_rows, a.shape[1],
-                1 if gated else 0, pair_offset, 1 if out.dtype == torch.float32 else 0, _p(out), ldo, _p(st), _stream())
+    _lib().call("wick_gemm_tc2", "pipliiiiiiplpp", _p(a), a.shape[0], _p(b), b.shape[0], b_rows, a.shape[1],
+                1 if gated else 0, pair_offset, 1 if out.dtype == torch.float32 else 0, 1 if accumulate else 0, _p(out), ldo,
+                _p(st), _stream())
 
 
 def _ceil16(n: int) -> int:
@@ -109,6 +111,16 @@ class Plan:
         if t:
             self._run(x, out, splits=splits)
         return out
+
+    def forward_add(self, x: torch.Tensor, residual: torch.Tensor) -> bool:
+        """residual [n, out] (float32) += x W^T, every element by one thread, where the
+        kernel for many tokens runs; False (and nothing done) otherwise."""
+        t = x.shape[0]
+        if self.gated or t < PAIR_MIN or residual.dtype != torch.float32 or not residual.is_contiguous() \
+                or tuple(residual.shape) != (t, self.n_out):
+            return False
+        gemm_tc_pair(x, self.w, self.n_out, out=residual, ldo=self.n_out, accumulate=True)
+        return True
 
     def _run(self, x: torch.Tensor, out: torch.Tensor, splits: int) -> None:
         t = x.shape[0]

@@ -146,7 +146,12 @@ class Mixer(Part):
         cache: the view of this schedule entry's cache storage for this batch
         (None if :meth:`cache_need` is None).  write_cache is False when the
         entry reads an earlier entry's cache.
-        Returns float32 [splits, tokens, width], to be summed into the residual."""
+        Returns float32 [splits, tokens, width], to be summed into the residual.
+
+        A mixer (or feed-forward) whose class sets ``ADDS_TO_RESIDUAL = True`` is
+        also given ``residual=`` (the float32 residual stream [tokens, width]); it
+        may add its result to it itself (each element once, in a fixed order) and
+        return None."""
         raise NotImplementedError
 
 

@@ -56,11 +56,15 @@ class Linear:
                 return tc.forward(x, out_dtype)
         return ops.gemm_simt(x, self.weight, out_dtype, gated=self.gated)
 
-    def forward_delta(self, x: torch.Tensor) -> torch.Tensor:
+    def forward_delta(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """[n, in] -> float32 [splits, n, out]: partial sums over slices of the
-        inner dimension, to be added up (in index order) by whoever consumes them."""
+        inner dimension, to be added up (in index order) by whoever consumes them.
+        With ``residual`` (float32 [n, out]) the product may instead be added to it
+        by the kernel itself (each element by one thread); then None is returned."""
         if self.ctx.dtype == torch.bfloat16:
             tc = self._tensor_core()
             if tc is not None:
+                if residual is not None and tc.forward_add(x, residual):
+                    return None
                 return tc.forward_delta(x)
         return ops.gemm_simt(x, self.weight, torch.float32).unsqueeze(0)

@@ -152,7 +152,9 @@ class GQAttention(Mixer):
     def weight_bytes(self):
         return self.qkv.weight_bytes() + self.o.weight_bytes() + (2 * self.head_dim * 4 if self.q_norm else 0)
 
-    def forward(self, x, batch, cache, write_cache):
+    ADDS_TO_RESIDUAL = True
+
+    def forward(self, x, batch, cache, write_cache, residual=None):
         inv_freq = self.position.rotary_inv_freq()
         if inv_freq is None and not isinstance(self.position, NoPosition):
             q = self._encode_unfused(x, batch, cache, write_cache)
@@ -169,7 +171,7 @@ class GQAttention(Mixer):
                     k_weight=self.k_norm.weight if self.k_norm else None,
                     eps=self.q_norm.eps if self.q_norm else 0.0, cos=cos, sin=sin, kv=cache.kv, batch=batch,
                     scale=self.scale, write_kv=write_cache, max_kv_len=batch.kv_bound)
-                return self.o.forward_delta(att.view(batch.n_tokens, self.q_dim))
+                return self.o.forward_delta(att.view(batch.n_tokens, self.q_dim), residual)
             q = ops.qk_norm_rope_append(
                 qkv, self.heads, self.kv_heads, self.head_dim,
                 q_weight=self.q_norm.weight if self.q_norm else None,
@@ -186,7 +188,7 @@ class GQAttention(Mixer):
                                        max_kv_len=batch.kv_bound)
         else:
             att = ops.attention_prompt(q, cache.kv, batch, self.scale)
-        return self.o.forward_delta(att.view(batch.n_tokens, self.q_dim))
+        return self.o.forward_delta(att.view(batch.n_tokens, self.q_dim), residual)
 
 
     def _encode_unfused(self, x, batch, cache, write_cache):
@@ -236,15 +238,19 @@ class GatedMLP(FeedForward):
     def weight_bytes(self):
         return self.gate_up.weight_bytes() + self.down.weight_bytes()
 
-    def forward(self, x, batch):
+    ADDS_TO_RESIDUAL = True
+
+    def forward(self, x, batch, residual=None):
         act = self.gate_up.forward(x, self.ctx.dtype)                   # [n, intermediate]
-        return self.down.forward_delta(act)
+        return self.down.forward_delta(act, residual)
 
 
 # ---------------------------------------------------------------------------
 class PreNormResidual(Block):
-    """x += mixer(norm1(x)); x += ffn(norm2(x)) — each addition is left pending
-    so that the following norm's kernel performs it."""
+    """x += mixer(norm1(x)); x += ffn(norm2(x)).  An addition is either left pending,
+    so that the following norm's kernel performs it, or done by the part itself: a
+    part whose class says ``ADDS_TO_RESIDUAL`` is handed the residual stream and
+    returns None when it has added its result to it (its last kernel did)."""
 
     def forward(self, h, batch, cache, write_cache):
         dt = self.ctx.dtype
@@ -252,9 +258,16 @@ class PreNormResidual(Block):
             xn = self.mixer_norm.add_forward(h.x, h.pending, dt)
         else:
             xn = self.mixer_norm.forward(h.x, dt)
-        d = as_splits(self.mixer.forward(xn, batch, cache, write_cache))
-        xn = self.ffn_norm.add_forward(h.x, d, dt)
-        h.pending = as_splits(self.ffn.forward(xn, batch))
+        if getattr(self.mixer, "ADDS_TO_RESIDUAL", False):
+            d = self.mixer.forward(xn, batch, cache, write_cache, residual=h.x)
+        else:
+            d = self.mixer.forward(xn, batch, cache, write_cache)
+        xn = self.ffn_norm.forward(h.x, dt) if d is None else self.ffn_norm.add_forward(h.x, as_splits(d), dt)
+        if getattr(self.ffn, "ADDS_TO_RESIDUAL", False):
+            d = self.ffn.forward(xn, batch, residual=h.x)
+        else:
+            d = self.ffn.forward(xn, batch)
+        h.pending = None if d is None else as_splits(d)
         return h
 
 
