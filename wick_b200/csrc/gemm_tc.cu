@@ -49,6 +49,7 @@ struct GemmParams {
     int transposed;                // 0: out[m * ldo + n], 1: out[n * ldo + m]
     int out_f32;
     int total_tiles, grid_m, grid_n;   // tiles = grid_m * grid_n * splits, the m tile varying fastest
+    int a_packed, b_packed;        // that operand is stored as tiles of 128 rows x 64 columns (see wick_gemm_tc)
     int a_static;                  // A is never written by a kernel (weights): it may be fetched before the
     int b_static;                  //   preceding kernel has finished; likewise B
     long long ldo;
@@ -141,18 +142,26 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int w = w_first; w < w_end && ok; w += w_step) {
                 int m0, n0, kb_begin, n_kb, z;
                 tile_coords(w, m0, n0, kb_begin, n_kb, z);
+                // Coordinates of the box that holds rows row.. of k-block kb: in a row-major
+                // operand (kb * 64, row); in a packed one the tile (row / 128, kb) lies as
+                // 128 contiguous lines of 128 bytes.
+                auto load = [&](const CUtensorMap* map, int packed, int s, void* dst, int kb, int row) {
+                    if (packed) tma_load_2d(map, &full_bar[s], dst, 0, ((row >> 7) * p.k_blocks + kb) * 128 + (row & 127));
+                    else tma_load_2d(map, &full_bar[s], dst, kb * BK, row);
+                };
                 auto load_a = [&](int i, int s) {
                     uint8_t* st = tiles + (size_t)s * stage_bytes;
-                    const int kx = (kb_begin + i) * BK;
-                    tma_load_2d(&map_a, &full_bar[s], st, kx, m0);
-                    if (a_tiles == 2) tma_load_2d(&map_a, &full_bar[s], st + a_bytes, kx, m0 + p.pair_offset);
-                    if (GATED == 3) tma_load_2d(&map_a, &full_bar[s], st + a_bytes / 2, kx, m0 + p.pair_offset);   // 64-row boxes
+                    const int kb = kb_begin + i;
+                    load(&map_a, p.a_packed, s, st, kb, m0);
+                    if (a_tiles == 2) load(&map_a, p.a_packed, s, st + a_bytes, kb, m0 + p.pair_offset);
+                    if (GATED == 3) load(&map_a, p.a_packed, s, st + a_bytes / 2, kb, m0 + p.pair_offset);   // 64-row boxes
                 };
                 auto load_b = [&](int i, int s) {
                     uint8_t* sb = tiles + (size_t)s * stage_bytes + a_tiles * a_bytes;
-                    const int kx = (kb_begin + i) * BK;
-                    tma_load_2d(&map_b, &full_bar[s], sb, kx, n0);
-                    if (b_tiles == 2) tma_load_2d(&map_b, &full_bar[s], sb + b_bytes, kx, n0 + p.pair_offset);
+                    const int kb = kb_begin + i;
+                    load(&map_b, p.b_packed, s, sb, kb, n0);
+                    if (p.b_packed && p.bn > 128) load(&map_b, p.b_packed, s, sb + 128 * BK * 2, kb, n0 + 128);   // 256 rows: two tiles
+                    if (b_tiles == 2) load(&map_b, p.b_packed, s, sb + b_bytes, kb, n0 + p.pair_offset);
                 };
                 int i = 0;
                 if (it == 0) {
@@ -364,10 +373,15 @@ using namespace wick;
 // splits > 1 needs out_f32; partial s lies split_stride elements after s - 1.
 // a_static / b_static: that operand is never written by any kernel (weights), so
 // the kernel may fetch it before the kernel launched before it has finished.
+// a_packed / b_packed: that operand is not row-major but stored as [rows / 128][ceil(k / 64)]
+// tiles of 128 rows x 64 columns, each tile contiguous (16 KB), rows and columns padded
+// with zeros (a gated pair: each half padded on its own, pair_offset counts padded rows);
+// a_total_rows / b_total_rows then count padded rows.  A weight tile then comes from DRAM as
+// one contiguous piece instead of 128 pieces of 128 bytes.
 // status: device int that receives a non-zero code if a wait inside the kernel gave up.
 WICK_API int wick_gemm_tc(const void* a, long long a_total_rows, int a_rows, const void* b, long long b_total_rows,
                           int b_rows, int k, int bn, int gated, int pair_offset, int transposed, int out_f32,
-                          int a_static, int b_static, void* out, long long ldo, int splits, long long split_stride, int max_smem_bytes, int* status,
+                          int a_static, int b_static, int a_packed, int b_packed, void* out, long long ldo, int splits, long long split_stride, int max_smem_bytes, int* status,
                           void* stream) {
     WICK_REQUIRE(bn % 16 == 0 && bn >= 16 && bn <= 256, "gemm_tc: tile width %d must be a multiple of 16 in [16, 256]", bn);
     WICK_REQUIRE(!(gated == 2 && bn > 128) , "gemm_tc: a gated pair needs two accumulators: tile width <= 128");
@@ -383,8 +397,12 @@ WICK_API int wick_gemm_tc(const void* a, long long a_total_rows, int a_rows, con
     const int per_split = ceil_div(k_blocks, splits);
     WICK_REQUIRE((long long)(splits - 1) * per_split < k_blocks, "gemm_tc: a split would be empty");
     CUtensorMap map_a, map_b;
-    if (int e = make_map(&map_a, a, a_total_rows, k, gated == 3 ? BM / 2 : BM)) return e;
-    if (int e = make_map(&map_b, b, b_total_rows, k, bn)) return e;
+    WICK_REQUIRE(!a_packed || a_total_rows % 128 == 0, "gemm_tc: a packed operand has a multiple of 128 rows");
+    WICK_REQUIRE(!b_packed || (b_total_rows % 128 == 0 && (bn <= 128 || bn == 256)), "gemm_tc: a packed narrow operand comes in tiles of 128 rows");
+    if (int e = a_packed ? make_map(&map_a, a, a_total_rows * k_blocks, 64, gated == 3 ? BM / 2 : BM)
+                         : make_map(&map_a, a, a_total_rows, k, gated == 3 ? BM / 2 : BM)) return e;
+    if (int e = b_packed ? make_map(&map_b, b, b_total_rows * k_blocks, 64, bn < 128 ? bn : 128)
+                         : make_map(&map_b, b, b_total_rows, k, bn)) return e;
     const int stage_bytes = (gated == 1 ? 2 : 1) * BM * BK * 2 + (gated == 2 ? 2 : 1) * bn * BK * 2;
     int budget = max_smem_bytes > 0 ? max_smem_bytes : 200 * 1024;
     if (budget > 208 * 1024) budget = 208 * 1024;     // 227 KB per block minus the static arrays
@@ -397,7 +415,7 @@ WICK_API int wick_gemm_tc(const void* a, long long a_total_rows, int a_rows, con
     p.a_rows = a_rows; p.b_rows = b_rows; p.bn = bn; p.k_blocks = k_blocks; p.k_blocks_per_split = per_split;
     p.stages = stages; p.gated = gated; p.pair_offset = pair_offset; p.transposed = transposed; p.out_f32 = out_f32;
     p.ldo = ldo; p.split_stride = split_stride; p.out = out; p.status = status;
-    p.a_static = a_static; p.b_static = b_static;
+    p.a_static = a_static; p.b_static = b_static; p.a_packed = a_packed; p.b_packed = b_packed;
     p.grid_m = ceil_div(a_rows, gated == 3 ? BM / 2 : BM);
     p.grid_n = ceil_div(b_rows, bn);
     const long long total = (long long)p.grid_m * p.grid_n * splits;

@@ -41,6 +41,7 @@ constexpr uint32_t kPeerMask = 0xFEFFFFFFu;            // clears the bit that te
 struct Params {
     int a_rows, b_rows;            // valid rows of A; outputs per row (for a gated pair: of ONE half)
     int k_blocks;
+    int b_packed;                  // B is stored as contiguous tiles of 128 rows x 64 columns (see wick_gemm_tc)
     int gated;                     // 0 plain, 1 gate rows in block 0's B half and up rows in block 1's
     int pair_offset;               // row offset of the up half inside B
     int out_f32;
@@ -151,7 +152,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     if (!mbar_wait(&empty_bar[s], (round & 1) ^ 1, &abort_flag, p.status, 1)) { ok = false; break; }
                     uint8_t* st = tiles + (size_t)s * STAGE_BYTES;
                     if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * STAGE_BYTES);
-                    tma_load_2d_pair(&map_b, &full_bar[s], st + BM * BK * 2, i * BK, b_row);   // weights: no kernel writes them
+                    if (p.b_packed) tma_load_2d_pair(&map_b, &full_bar[s], st + BM * BK * 2, 0, ((b_row >> 7) * p.k_blocks + i) * 128);
+                    else tma_load_2d_pair(&map_b, &full_bar[s], st + BM * BK * 2, i * BK, b_row);   // weights: no kernel writes them
                     if (first) { pdl_wait(); first = false; }                                  // activations: after the producer of A
                     tma_load_2d_pair(&map_a, &full_bar[s], st, i * BK, a_row);
                 }
@@ -309,19 +311,22 @@ using namespace wick;
 // a: activations [a_rows, k] bf16; b: weights [b_total_rows, k] bf16; out[m * ldo + n], n < b_rows.
 // gated: b holds gate rows [0, b_rows) and up rows [pair_offset, pair_offset + b_rows); the
 // output is silu(a gate^T) * (a up^T).  accumulate (plain float32 output only): out += the product
-// (every element by one thread: no atomics).  status as in wick_gemm_tc.
+// (every element by one thread: no atomics).  b_packed: b in the tiled form described at wick_gemm_tc.
+// status as in wick_gemm_tc.
 WICK_API int wick_gemm_tc2(const void* a, int a_rows, const void* b, long long b_total_rows, int b_rows, int k, int gated,
-                           int pair_offset, int out_f32, int accumulate, void* out, long long ldo, int* status, void* stream) {
+                           int pair_offset, int out_f32, int accumulate, int b_packed, void* out, long long ldo, int* status, void* stream) {
     using namespace pair;
     WICK_REQUIRE(a_rows > 0 && b_rows > 0 && k > 0, "gemm_tc2: bad sizes");
     WICK_REQUIRE(gated == 0 || gated == 1, "gemm_tc2: bad options");
     WICK_REQUIRE(!accumulate || (out_f32 && !gated), "gemm_tc2: accumulation goes with a plain float32 output");
     CUtensorMap map_a, map_b;
     if (int e = make_bf16_map(&map_a, a, a_rows, k, BM, "gemm_tc2")) return e;
-    if (int e = make_bf16_map(&map_b, b, b_total_rows, k, BNH, "gemm_tc2")) return e;
+    WICK_REQUIRE(!b_packed || (b_total_rows % 128 == 0 && pair_offset % 128 == 0), "gemm_tc2: a packed operand comes in tiles of 128 rows");
+    if (int e = b_packed ? make_bf16_map(&map_b, b, b_total_rows * ceil_div(k, BK), 64, BNH, "gemm_tc2")
+                         : make_bf16_map(&map_b, b, b_total_rows, k, BNH, "gemm_tc2")) return e;
     Params p;
     p.a_rows = a_rows; p.b_rows = b_rows; p.k_blocks = ceil_div(k, BK); p.gated = gated; p.pair_offset = pair_offset;
-    p.out_f32 = out_f32; p.ldo = ldo; p.out = out; p.status = status;
+    p.out_f32 = out_f32; p.ldo = ldo; p.out = out; p.status = status; p.b_packed = b_packed;
     p.grid_m = ceil_div(a_rows, 2 * BM);
     p.grid_n = ceil_div(b_rows, gated ? BNH : BN);
     const long long total = (long long)p.grid_m * p.grid_n;

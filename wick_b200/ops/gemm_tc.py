@@ -39,42 +39,80 @@ def _lib() -> _Lib:
     return lib
 
 
-_SIG = "plipliiiiiiiiiplilipp"
+_SIG = "plipliiiiiiiiiiiplilipp"
 
 
 def gemm_tc(a: torch.Tensor, a_rows: int, b: torch.Tensor, b_rows: int, *, bn: int, out: torch.Tensor, ldo: int,
             gated: int = 0, pair_offset: int = 0, transposed: bool = False, splits: int = 1, split_stride: int = 0,
-            max_smem: int = 0, a_static: bool = False, b_static: bool = False) -> None:
-    """The raw kernel call (see ``wick_gemm_tc`` in gemm_tc.cu)."""
-    for nm, t in (("a", a), ("b", b)):
-        if not (t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous() and t.dim() == 2):
-            raise KernelError(f"gemm_tc: {nm} must be a contiguous 2-D bfloat16 CUDA tensor")
-    if a.shape[1] != b.shape[1]:
-        raise KernelError(f"gemm_tc: inner sizes differ: {a.shape[1]} and {b.shape[1]}")
+            max_smem: int = 0, a_static: bool = False, b_static: bool = False, a_packed: bool = False,
+            b_packed: bool = False, k: Optional[int] = None) -> None:
+    """The raw kernel call (see ``wick_gemm_tc`` in gemm_tc.cu).  A packed operand is a
+    :func:`pack` result [tiles, k blocks, 128, 64]; ``k`` then names the inner size."""
+    def rows_and_k(nm, t, packed):
+        if not (t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous()):
+            raise KernelError(f"gemm_tc: {nm} must be a contiguous bfloat16 CUDA tensor")
+        if packed:
+            if t.dim() != 4 or tuple(t.shape[2:]) != (128, 64):
+                raise KernelError(f"gemm_tc: packed {nm} must be [tiles, k blocks, 128, 64]")
+            return t.shape[0] * 128, None
+        if t.dim() != 2:
+            raise KernelError(f"gemm_tc: {nm} must be 2-D")
+        return t.shape[0], t.shape[1]
+    ra, ka = rows_and_k("a", a, a_packed)
+    rb, kb = rows_and_k("b", b, b_packed)
+    k = k if k is not None else (ka if ka is not None else kb)
+    for kk in (ka, kb):
+        if kk is not None and kk != k:
+            raise KernelError(f"gemm_tc: inner sizes differ: {ka} and {kb} (k = {k})")
     if out.dtype not in (torch.float32, torch.bfloat16) or not out.is_contiguous():
         raise KernelError("gemm_tc: out must be contiguous float32 or bfloat16")
     st = status_tensor(a.device)
-    _lib().call("wick_gemm_tc", _SIG, _p(a), a.shape[0], a_rows, _p(b), b.shape[0], b_rows, a.shape[1], bn, gated,
+    _lib().call("wick_gemm_tc", _SIG, _p(a), ra, a_rows, _p(b), rb, b_rows, k, bn, gated,
                 pair_offset, 1 if transposed else 0, 1 if out.dtype == torch.float32 else 0, 1 if a_static else 0,
-                1 if b_static else 0, _p(out), ldo, splits,
+                1 if b_static else 0, 1 if a_packed else 0, 1 if b_packed else 0, _p(out), ldo, splits,
                 split_stride, max_smem, _p(st), _stream())
 
 
+def pack(w: torch.Tensor, gated: bool = False) -> torch.Tensor:
+    """A [rows, k] matrix as [tiles, ceil(k / 64), 128, 64]: tiles of 128 rows x 64
+    columns, each contiguous, rows and columns padded with zeros; the two halves of a
+    gated pair are padded each on its own.  A kernel then fetches a weight tile as one
+    contiguous 16 KB piece of DRAM instead of 128 pieces of 128 bytes."""
+    rows, k = w.shape
+    halves = [w[:rows // 2], w[rows // 2:]] if gated else [w]
+    kp = (k + 63) // 64 * 64
+    out = []
+    for h in halves:
+        r = h.shape[0]
+        rp = (r + 127) // 128 * 128
+        if rp != r or kp != k:
+            t = torch.zeros((rp, kp), dtype=w.dtype, device=w.device)
+            t[:r, :k] = h
+        else:
+            t = h
+        out.append(t.view(rp // 128, 128, kp // 64, 64).permute(0, 2, 1, 3))
+    return torch.cat(out, 0).contiguous() if len(out) > 1 else out[0].contiguous()
+
+
 def gemm_tc_pair(a: torch.Tensor, b: torch.Tensor, b_rows: int, *, out: torch.Tensor, ldo: int, gated: bool = False,
-                 pair_offset: int = 0, accumulate: bool = False) -> None:
+                 pair_offset: int = 0, accumulate: bool = False, b_packed: bool = False) -> None:
     """The kernel for pairs of thread blocks (see ``wick_gemm_tc2`` in gemm_tc2.cu): out[m, n] = a[m] . b[n],
     or out[m, n] += ... with ``accumulate`` (float32 output)."""
     for nm, t in (("a", a), ("b", b)):
-        if not (t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous() and t.dim() == 2):
-            raise KernelError(f"gemm_tc_pair: {nm} must be a contiguous 2-D bfloat16 CUDA tensor")
-    if a.shape[1] != b.shape[1]:
+        if not (t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous()):
+            raise KernelError(f"gemm_tc_pair: {nm} must be a contiguous bfloat16 CUDA tensor")
+    if a.dim() != 2 or (b.dim() != 2 if not b_packed else (b.dim() != 4 or tuple(b.shape[2:]) != (128, 64))):
+        raise KernelError("gemm_tc_pair: a must be 2-D, b 2-D or a packed [tiles, k blocks, 128, 64]")
+    if not b_packed and a.shape[1] != b.shape[1]:
         raise KernelError(f"gemm_tc_pair: inner sizes differ: {a.shape[1]} and {b.shape[1]}")
+    if b_packed and b.shape[1] != (a.shape[1] + 63) // 64:
+        raise KernelError(f"gemm_tc_pair: packed b has {b.shape[1]} k blocks, a an inner size of {a.shape[1]}")
     if out.dtype not in (torch.float32, torch.bfloat16) or not out.is_contiguous():
         raise KernelError("gemm_tc_pair: out must be contiguous float32 or bfloat16")
     st = status_tensor(a.device)
-    _lib().call("wick_gemm_tc2", "pipliiiiiiplpp", _p(a), a.shape[0], _p(b), b.shape[0], b_rows, a.shape[1],
-                1 if gated else 0, pair_offset, 1 if out.dtype == torch.float32 else 0, 1 if accumulate else 0, _p(out), ldo,
-                _p(st), _stream())
+    _lib().call("wick_gemm_tc2", "pipliiiiiiiplpp", _p(a), a.shape[0], _p(b), b.shape[0] * 128 if b_packed else b.shape[0],
+                b_rows, a.shape[1], 1 if gated else 0, pair_offset, 1 if out.dtype == torch.float32 else 0,
+                1 if accumulate else 0, 1 if b_packed else 0, _p(out), ldo, _p(st), _stream())
 
 
 def _ceil16(n: int) -> int:
@@ -82,11 +120,15 @@ def _ceil16(n: int) -> int:
 
 
 class Plan:
+    """Holds the matrix in the packed form (:func:`pack`); the row-major original is
+    not kept."""
+
     def __init__(self, weight: torch.Tensor, gated: bool):
-        self.w = weight
         self.gated = gated
         self.rows, self.k = weight.shape
         self.n_out = self.rows // 2 if gated else self.rows
+        self.w = pack(weight, gated)
+        self.pair_offset = (self.n_out + 127) // 128 * 128            # in padded rows
         k_blocks = (self.k + 63) // 64
         tiles = (self.n_out + 127) // 128
         # Decode: about two blocks per SM (just under 2 x 148) stream best; every
@@ -119,7 +161,7 @@ class Plan:
         if self.gated or t < PAIR_MIN or residual.dtype != torch.float32 or not residual.is_contiguous() \
                 or tuple(residual.shape) != (t, self.n_out):
             return False
-        gemm_tc_pair(x, self.w, self.n_out, out=residual, ldo=self.n_out, accumulate=True)
+        gemm_tc_pair(x, self.w, self.n_out, out=residual, ldo=self.n_out, accumulate=True, b_packed=True)
         return True
 
     def _run(self, x: torch.Tensor, out: torch.Tensor, splits: int) -> None:
@@ -129,15 +171,18 @@ class Plan:
             # other's streaming.  A gated pair shares one 128-row tile (64 gate rows,
             # 64 up rows), which doubles the number of blocks.
             gemm_tc(self.w, self.n_out, x, t, bn=_ceil16(t), out=out, ldo=self.n_out,
-                    gated=3 if self.gated else 0, pair_offset=self.n_out, transposed=True, splits=splits,
-                    split_stride=t * self.n_out, max_smem=100 * 1024, a_static=True)
+                    gated=3 if self.gated else 0, pair_offset=self.pair_offset, transposed=True, splits=splits,
+                    split_stride=t * self.n_out, max_smem=100 * 1024, a_static=True, a_packed=True, k=self.k)
         elif t >= PAIR_MIN and splits == 1:
-            gemm_tc_pair(x, self.w, self.n_out, out=out, ldo=self.n_out, gated=self.gated, pair_offset=self.n_out)
+            gemm_tc_pair(x, self.w, self.n_out, out=out, ldo=self.n_out, gated=self.gated, pair_offset=self.pair_offset,
+                         b_packed=True)
         else:
             bn = min(128 if self.gated else 256, _ceil16(self.n_out))
+            if bn > 128:
+                bn = 256                               # two packed tiles of 128 rows
             gemm_tc(x, t, self.w, self.n_out, bn=bn, out=out, ldo=self.n_out, gated=2 if self.gated else 0,
-                    pair_offset=self.n_out, transposed=False, splits=splits, split_stride=t * self.n_out,
-                    max_smem=200 * 1024, b_static=True)
+                    pair_offset=self.pair_offset, transposed=False, splits=splits, split_stride=t * self.n_out,
+                    max_smem=200 * 1024, b_static=True, b_packed=True, k=self.k)
 
 
 def plan_for(weight: torch.Tensor, gated: bool = False) -> Optional[Plan]:

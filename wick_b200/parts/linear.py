@@ -36,6 +36,8 @@ class Linear:
                              f"[{self.out_features}, {self.in_features}] expected")
         self.weight = w.contiguous()
         self._tc = None
+        if self.ctx.dtype == torch.bfloat16 and self._tensor_core() is not None:
+            self.weight = None                 # the plan holds the matrix in its packed form
 
     def weight_bytes(self) -> int:
         return self.out_features * self.in_features * (2 if self.ctx.dtype == torch.bfloat16 else 4)
