@@ -7,17 +7,16 @@
 //   * a producer thread fetches the query rows once and the key and value pages
 //     through a ring of six tiles (TMA, 64 x 64 boxes, 128-byte swizzle); a key
 //     tile is free again as soon as its scores are computed;
-//   * an issuing thread computes S = Q K^T into one of two 128-column buffers
-//     of tensor memory and accumulates O += P V (the values are the MN-major
-//     operand: their rows are keys);
-//   * two groups of four warps take the key blocks in turn (even blocks, odd
-//     blocks), each with a score buffer, an accumulator O, a maximum and a sum of
-//     its own, so that one group's exponentials overlap the other's waits; a
-//     thread owns one query row: it reads S from tensor memory, scales, masks
-//     (a key is visible up to the token's own position), and writes P as pairs
-//     of bfloat16 back into tensor memory over the scores it came from, where
-//     the second product takes it from.  At the end the two groups' results
-//     are merged like the splits of a decode step.
+//   * an issuing thread computes S = Q K^T into one of three 128-column buffers
+//     of tensor memory, up to three blocks ahead of the softmax, and accumulates
+//     O += P V (the values are the MN-major operand: their rows are keys);
+//   * eight warps own one query row per pair of threads (64 keys of a block each;
+//     the row's maximum crosses through shared memory): they read S from tensor
+//     memory, scale, mask (a key is visible up to the token's own position), and
+//     write P as pairs of bfloat16 back into tensor memory over the scores it
+//     came from, where the second product takes it from.  With three buffers the
+//     softmax of the next block never waits for a product: what bounds a block
+//     is the 16 instructions the tensor core takes for it (one every ~93 clocks).
 // O and the sum are scaled by a maximum that follows the true running maximum
 // lazily: only when a block's maximum exceeds it by more than 8 (in units of
 // log2 e) is O rescaled in tensor memory, so that after the first blocks of a row
@@ -53,9 +52,11 @@ constexpr int PANEL_BYTES = 128 * 128;                 // 128 rows of 128 bytes
 constexpr int TILE_BYTES = PANELS * PANEL_BYTES;       // Q, or one block of keys or of values
 constexpr int NSLOT = 6;                               // key / value tiles in flight (3 blocks)
 constexpr int SMEM_BYTES = TILE_BYTES + NSLOT * TILE_BYTES + 1024;
-constexpr int THREADS = 320;                           // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-5 and 6-9: softmax groups
-constexpr uint32_t TMEM_COLS = 512;                    // S0 | S1 | O0 | O1; P (bfloat16 pairs) takes the place of the
-constexpr uint32_t COL_S = 0, COL_O = 256;             // first 64 columns of the S buffer it was computed from
+constexpr int THREADS = 320;                           // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-9: softmax
+constexpr int NBUF = 3;                                // score buffers
+constexpr int HALF_K = BK / 2;                         // keys of a block that one softmax thread handles
+constexpr uint32_t TMEM_COLS = 512;                    // S0 | S1 | S2 | O; P (bfloat16 pairs) takes the place of the
+constexpr uint32_t COL_S = 0, COL_O = NBUF * BK;       // first 64 columns of the S buffer it was computed from
 typedef __nv_bfloat16 bf16;
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
@@ -142,7 +143,8 @@ attn_prompt_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_co
                       float scale, int* status) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t q_full, full[NSLOT], empty[NSLOT];
-    __shared__ uint64_t s_full[2], p_full[2], pv_done[2], fin_bar[4];
+    __shared__ uint64_t s_full[NBUF], p_full[NBUF], pv_done[2], x_bar[4];   // pv_done: even blocks, odd blocks
+    __shared__ bf16 mx_x[2][2][BQ];                            // the maxima the two halves of a row tell each other
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
 
@@ -171,12 +173,15 @@ attn_prompt_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_co
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < NBUF; ++i) {
             mbar_init(&s_full[i], 1);
-            mbar_init(&p_full[i], 4);                              // one arrival per warp of the group
-            mbar_init(&pv_done[i], 1);
+            // One arrival per softmax warp; a barrier per score buffer, since a warp may be up to
+            // two blocks ahead of another (never three: the scores of block j + 3 wait for P V of block j).
+            mbar_init(&p_full[i], 8);
         }
-        for (int i = 0; i < 4; ++i) mbar_init(&fin_bar[i], 2);     // the two warps that share 32 rows
+        mbar_init(&pv_done[0], 1);
+        mbar_init(&pv_done[1], 1);
+        for (int i = 0; i < 4; ++i) mbar_init(&x_bar[i], 2);       // the two warps that share 32 rows
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -210,7 +215,7 @@ attn_prompt_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_co
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
-        // Block j belongs to group j & 1: scores in S[j & 1], accumulator O[j & 1].
+        // Block j: scores in S[j % 3], all blocks accumulate into the one O.
         // (Measured on this part: the tensor core takes an instruction of this kind every
         // ~93 clocks at best, whatever its width up to N = 128; 16 of them make a block.)
         if (lane == 0) {
@@ -220,81 +225,89 @@ attn_prompt_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_co
             const uint32_t q_lo = desc_lo(smem_u32(q_s), 16);
             const uint32_t k_lo0 = desc_lo(smem_u32(kv_s), 16), v_lo0 = desc_lo(smem_u32(kv_s), PANEL_BYTES);
             auto issue_s = [&](int j) -> bool {
-                const int i = 2 * j, slot = i % NSLOT, g = j & 1;
+                const int i = 2 * j, slot = i % NSLOT, buf = j % NBUF;
                 if (!mbar_wait(&full[slot], (i / NSLOT) & 1, &abort_flag, status, 7)) return false;
                 tc_fence_after();
-                const uint32_t k_lo = k_lo0 + slot * (TILE_BYTES >> 4), d = tmem + COL_S + g * BK;
+                const uint32_t k_lo = k_lo0 + slot * (TILE_BYTES >> 4), d = tmem + COL_S + buf * BK;
                 static_for<0, HD / 16>([&](auto ks) {
                     constexpr uint32_t off = (((int)ks >> 2) * PANEL_BYTES + ((int)ks & 3) * 32) >> 4;
                     mma_ss<((int)ks > 0)>(d, q_lo + off, k_lo + off, idesc_s);
                 });
-                tc_commit(&s_full[g]);
+                tc_commit(&s_full[buf]);
                 tc_commit(&empty[slot]);                                     // the keys are read
                 return true;
             };
             bool ok = mbar_wait(&q_full, 0, &abort_flag, status, 7);
-            ok = ok && issue_s(0);
-            if (n_blk > 1) ok = ok && issue_s(1);
+            for (int j = 0; j < NBUF && j < n_blk && ok; ++j) ok = issue_s(j);
             for (int j = 0; j < n_blk && ok; ++j) {
-                const int i = 2 * j + 1, slot = i % NSLOT, g = j & 1, u = j >> 1;
-                ok = ok && mbar_wait(&p_full[g], u & 1, &abort_flag, status, 7);
+                const int i = 2 * j + 1, slot = i % NSLOT;
+                ok = ok && mbar_wait(&p_full[j % NBUF], (j / NBUF) & 1, &abort_flag, status, 7);
                 ok = ok && mbar_wait(&full[slot], (i / NSLOT) & 1, &abort_flag, status, 7);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t v_lo = v_lo0 + slot * (TILE_BYTES >> 4), d = tmem + COL_O + g * HD, pa = tmem + COL_S + g * BK;
-                if (u > 0) mma_ts<1>(d, pa, v_lo, idesc_o);
+                const uint32_t v_lo = v_lo0 + slot * (TILE_BYTES >> 4), d = tmem + COL_O, pa = tmem + COL_S + (j % NBUF) * BK;
+                if (j > 0) mma_ts<1>(d, pa, v_lo, idesc_o);
                 else mma_ts<0>(d, pa, v_lo, idesc_o);
                 static_for<1, BK / 16>([&](auto ks) { mma_ts<1>(d, pa + (int)ks * 8, v_lo + (int)ks * (2048 >> 4), idesc_o); });
-                tc_commit(&pv_done[g]);
+                tc_commit(&pv_done[j & 1]);
                 tc_commit(&empty[slot]);                                     // the values are read
-                if (j + 2 < n_blk) {
-                    // the group's next scores go where this block's P lies: only when it has been read
-                    ok = mbar_wait(&pv_done[g], u & 1, &abort_flag, status, 7) && issue_s(j + 2);
+                if (j + NBUF < n_blk) {
+                    // the scores of block j + 3 go where this block's P lies: only when it has been read
+                    ok = mbar_wait(&pv_done[j & 1], (j >> 1) & 1, &abort_flag, status, 7) && issue_s(j + NBUF);
                 }
             }
         }
     } else {
-        // ---------------- softmax: two groups, one query row per thread ----------------
-        const int g = (warp - 2) >> 2;                              // warps 2-5: even blocks, warps 6-9: odd blocks
-        const int quad = warp & 3;                                  // the 32 lanes of tensor memory this warp may touch
+        // ---------------- softmax: a query row per pair of threads ----------------
+        // Warps 2-5 take keys 0-63 of a block, warps 6-9 keys 64-127 of the same rows
+        // (a warp reads the 32 lanes of tensor memory given by its index modulo 4).
+        const int quad = warp & 3, half = (warp - 2) >> 2;
         const int r = quad * 32 + lane;
+        const int c_lo = half * HALF_K;
         const int q_pos = start + q0 + r;
         const int limit = min(q_pos, kv_len - 1);                   // last visible key position
         const float sl2 = scale * 1.4426950408889634f;
         const uint32_t lane_base = tmem + ((uint32_t)(quad * 32) << 16);
-        const uint32_t s_addr = lane_base + COL_S + g * BK, o_addr = lane_base + COL_O + g * HD;
-        float m = -INFINITY, l = 0.f;                               // the group's scaling maximum (units of log2 e) and sum
+        constexpr int OW = HD / 2;                                  // columns of O this thread rescales and stores
+        const uint32_t o_addr = lane_base + COL_O + half * OW;
+        // m: the maximum (in units of log2 e) that O and l are scaled by.  It follows
+        // the true running maximum lazily; l: this thread's part of the row's sum.
+        float m = -INFINITY, l = 0.f;
         bool ok = true;
-        for (int j = g; j < n_blk; j += 2) {
-            const int u = j >> 1, v_item = 2 * j + 1, v_slot = v_item % NSLOT;
-            ok = __all_sync(0xffffffffu, mbar_wait(&s_full[g], u & 1, &abort_flag, status, 7));
+        for (int j = 0; j < n_blk; ++j) {
+            const int buf = j % NBUF, xb = j & 1, v_item = 2 * j + 1, v_slot = v_item % NSLOT;
+            const uint32_t s_addr = lane_base + COL_S + buf * BK;
+            ok = __all_sync(0xffffffffu, mbar_wait(&s_full[buf], (j / NBUF) & 1, &abort_flag, status, 7));
             if (!ok) break;
             tc_fence_after();
-            const int key0 = j * BK;
-            const bool masked = key0 + BK - 1 > limit;
-            // pass 1: the block's maximum of the row
+            const int key0 = j * BK + c_lo;
+            float s[HALF_K];
+            tc_ld32_nowait(s_addr + c_lo, reinterpret_cast<uint32_t*>(s));
+            tc_ld32_nowait(s_addr + c_lo + 32, reinterpret_cast<uint32_t*>(s + 32));
+            tc_ld_wait();
+            if (key0 + HALF_K - 1 > limit) {
+#pragma unroll
+                for (int i = 0; i < HALF_K; ++i)
+                    if (key0 + i > limit) s[i] = -INFINITY;
+            }
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int h = 0; h < BK; h += 64) {
-                float s[64];
-                __syncwarp();
-                tc_ld32_nowait(s_addr + h, reinterpret_cast<uint32_t*>(s));
-                tc_ld32_nowait(s_addr + h + 32, reinterpret_cast<uint32_t*>(s + 32));
-                tc_ld_wait();
-                if (masked) {
-#pragma unroll
-                    for (int i = 0; i < 64; ++i)
-                        if (key0 + h + i > limit) s[i] = -INFINITY;
-                }
-#pragma unroll
-                for (int i = 0; i < 64; i += 4) {
-                    mx4[0] = fmaxf(mx4[0], s[i]);
-                    mx4[1] = fmaxf(mx4[1], s[i + 1]);
-                    mx4[2] = fmaxf(mx4[2], s[i + 2]);
-                    mx4[3] = fmaxf(mx4[3], s[i + 3]);
-                }
+            for (int i = 0; i < HALF_K; i += 4) {
+                mx4[0] = fmaxf(mx4[0], s[i]);
+                mx4[1] = fmaxf(mx4[1], s[i + 1]);
+                mx4[2] = fmaxf(mx4[2], s[i + 2]);
+                mx4[3] = fmaxf(mx4[3], s[i + 3]);
             }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2;
+            // The row's other half: through shared memory and the pair's barrier.  Both sides
+            // round to bfloat16, so that both scale by the same number (the scaling maximum
+            // need not be the exact one).
+            const bf16 mx_mine = __float2bfloat16_rn(fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])));
+            mx_x[xb][half][r] = mx_mine;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&x_bar[quad]);
+            ok = __all_sync(0xffffffffu, mbar_wait(&x_bar[quad], j & 1, &abort_flag, status, 7));
+            if (!ok) break;
+            const float mx = fmaxf(__bfloat162float(mx_mine), __bfloat162float(mx_x[xb][half ^ 1][r])) * sl2;
             const bool grow = mx > m + 8.0f;
             float alpha = 1.0f;
             if (grow) {
@@ -302,14 +315,17 @@ attn_prompt_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_co
                 m = mx;
             }
             const float neg_m = m == -INFINITY ? 0.f : -m;          // a row that sees no key yet
-            if (u > 0) {
-                // the group's last product is in O
-                ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[g], (u - 1) & 1, &abort_flag, status, 7));
+            if (j > 0 && __any_sync(0xffffffffu, grow)) {
+                // Rare.  O must hold the product of the block before.  (Its barrier serves every other
+                // block; that the scores of this block exist says that the product of block j - 3, the
+                // barrier's phase before, is complete: the parity is unambiguous although most blocks
+                // never wait here.)
+                ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[(j - 1) & 1], ((j - 1) >> 1) & 1, &abort_flag, status, 7));
                 if (!ok) break;
                 tc_fence_after();
-                if (__any_sync(0xffffffffu, grow)) {
+                {
 #pragma unroll
-                    for (int c = 0; c < HD; c += 32) {
+                    for (int c = 0; c < OW; c += 32) {
                         uint32_t raw[32];
                         tc_ld32_nowait(o_addr + c, raw);
                         tc_ld_wait();
@@ -320,40 +336,26 @@ attn_prompt_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_co
                     tc_st_wait();
                 }
             }
-            // pass 2: probabilities, their sum, and P over the first 64 columns of the scores
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t packed[HALF_K / 2];
 #pragma unroll
-            for (int h = 0; h < BK; h += 64) {
-                float s[64];
-                __syncwarp();
-                tc_ld32_nowait(s_addr + h, reinterpret_cast<uint32_t*>(s));
-                tc_ld32_nowait(s_addr + h + 32, reinterpret_cast<uint32_t*>(s + 32));
-                tc_ld_wait();
-                if (masked) {
-#pragma unroll
-                    for (int i = 0; i < 64; ++i)
-                        if (key0 + h + i > limit) s[i] = -INFINITY;
-                }
-                uint32_t packed[32];
-#pragma unroll
-                for (int i = 0; i < 64; i += 2) {
-                    const float p0 = ex2(fmaf(s[i], sl2, neg_m)), p1 = ex2(fmaf(s[i + 1], sl2, neg_m));
-                    sum4[(i >> 1) & 3] += p0 + p1;
-                    __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);     // key 2k in the low half, key 2k + 1 in the high half
-                    packed[i >> 1] = *reinterpret_cast<uint32_t*>(&hh);
-                }
-                __syncwarp();
-                tc_st32(s_addr + (h >> 1), packed);                      // keys h .. h + 63 -> columns h / 2 .. h / 2 + 31
+            for (int i = 0; i < HALF_K; i += 2) {
+                const float p0 = ex2(fmaf(s[i], sl2, neg_m)), p1 = ex2(fmaf(s[i + 1], sl2, neg_m));
+                sum4[(i >> 1) & 3] += p0 + p1;
+                __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);          // key 2k in the low half, key 2k + 1 in the high half
+                packed[i >> 1] = *reinterpret_cast<uint32_t*>(&hh);
             }
+            // P over the scores it came from (the other half has its scores in registers: it passed the pair's barrier)
+            tc_st32(s_addr + half * (HALF_K / 2), packed);
             tc_st_wait();
             l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
             // value rows that hold no token yet are made zero before they are multiplied
-            const int valid = kv_len - key0;
+            const int valid = kv_len - j * BK;
             if (valid < BK) {
                 ok = __all_sync(0xffffffffu, mbar_wait(&full[v_slot], (v_item / NSLOT) & 1, &abort_flag, status, 7));
                 if (!ok) break;
                 const int first = max(valid, 0);
-                for (int i = r; i < (BK - first) * (HD / 8); i += BQ) {
+                for (int i = threadIdx.x - 64; i < (BK - first) * (HD / 8); i += THREADS - 64) {
                     const int row = first + i / (HD / 8), chunk = i % (HD / 8);
                     *reinterpret_cast<uint4*>(kv_s + v_slot * TILE_BYTES + (chunk >> 3) * PANEL_BYTES + row * 128 +
                                               (((chunk & 7) ^ (row & 7)) << 4)) = make_uint4(0, 0, 0, 0);
@@ -362,61 +364,40 @@ attn_prompt_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_co
             }
             tc_fence_before();                                               // P and the rescaled O before it multiplies and accumulates
             __syncwarp();
-            if (lane == 0) mbar_arrive(&p_full[g]);
+            if (lane == 0) mbar_arrive(&p_full[buf]);
         }
-        // the group's last product
-        const int mine = (n_blk - g + 1) / 2;                       // blocks this group has handled
-        if (ok && mine > 0) ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[g], (mine - 1) & 1, &abort_flag, status, 7));
-        // (a group without a block still waits until the only scores are computed: the query tile is free then.
-        //  Otherwise the group's last product was issued after every score product, and has completed.)
-        if (ok && mine == 0) ok = __all_sync(0xffffffffu, mbar_wait(&s_full[0], 0, &abort_flag, status, 7));
+        // the last products, in their order (each wait with an unambiguous parity: see above)
+        if (ok && n_blk > 1) ok = __all_sync(0xffffffffu, mbar_wait(&pv_done[(n_blk - 2) & 1], ((n_blk - 2) >> 1) & 1, &abort_flag, status, 7));
+        ok = ok && __all_sync(0xffffffffu, mbar_wait(&pv_done[(n_blk - 1) & 1], ((n_blk - 1) >> 1) & 1, &abort_flag, status, 7));
         tc_fence_after();
-        // Merge of the two groups: each tells the other its maximum and sum (through the
-        // query tile's shared memory, which no product reads any more), then group 0
-        // stores the first half of the row's dims and group 1 the second.
-        float* ml_x = reinterpret_cast<float*>(q_s);                // [group][m, l][row]
+        float* l_x = reinterpret_cast<float*>(&mx_x[0][0][0]);       // free once every block's maxima have been read
         if (ok) {
-            ml_x[(g * 2 + 0) * BQ + r] = m;
-            ml_x[(g * 2 + 1) * BQ + r] = l;
-            tc_fence_before();
+            // the row's sum: this half's plus the other's, in a fixed order
+            l_x[half * BQ + r] = l;
             __syncwarp();
-            if (lane == 0) mbar_arrive(&fin_bar[quad]);
-            ok = __all_sync(0xffffffffu, mbar_wait(&fin_bar[quad], 0, &abort_flag, status, 7));
-            tc_fence_after();
+            if (lane == 0) mbar_arrive(&x_bar[quad]);
+            ok = __all_sync(0xffffffffu, mbar_wait(&x_bar[quad], n_blk & 1, &abort_flag, status, 7));
         }
         if (ok) {
-            const float m0 = ml_x[0 * BQ + r], l0 = ml_x[1 * BQ + r], m1 = ml_x[2 * BQ + r], l1 = ml_x[3 * BQ + r];
-            const float mm = fmaxf(m0, m1);
-            const float w0 = m0 == -INFINITY ? 0.f : ex2(m0 - mm), w1 = m1 == -INFINITY ? 0.f : ex2(m1 - mm);
-            const float l_row = w0 * l0 + w1 * l1;
+            // every lane takes part in the loads from tensor memory; only rows that exist are stored
+            const float l_row = l_x[r] + l_x[BQ + r];
             const bool store = r < rows && l_row > 0.f;
             const float inv = store ? 1.0f / l_row : 0.f;
-            const bool two = n_blk > 1;                             // with one block the second accumulator was never written
-            constexpr int OW = HD / 2;
-            bf16* dst = out + ((int64_t)(tok0 + q0 + r) * n_heads + head) * HD + g * OW;
+            bf16* dst = out + ((int64_t)(tok0 + q0 + r) * n_heads + head) * HD + half * OW;
 #pragma unroll
             for (int c = 0; c < OW; c += 32) {
-                // every lane takes part in the loads from tensor memory; only rows that exist are stored
-                uint32_t a[32], bb[32];
-                tc_ld32_nowait(lane_base + COL_O + g * OW + c, a);
-                if (two) tc_ld32_nowait(lane_base + COL_O + HD + g * OW + c, bb);
+                uint32_t raw[32];
+                tc_ld32_nowait(o_addr + c, raw);
                 tc_ld_wait();
                 if (store) {
 #pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4) {
+                    for (int g4 = 0; g4 < 4; ++g4) {
                         uint4 w;
                         __nv_bfloat162* hh = reinterpret_cast<__nv_bfloat162*>(&w);
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            const int e = 8 * q4 + 2 * i;
-                            float x0 = __uint_as_float(a[e]) * w0, x1 = __uint_as_float(a[e + 1]) * w0;
-                            if (two) {
-                                x0 = fmaf(__uint_as_float(bb[e]), w1, x0);
-                                x1 = fmaf(__uint_as_float(bb[e + 1]), w1, x1);
-                            }
-                            hh[i] = __floats2bfloat162_rn(x0 * inv, x1 * inv);
-                        }
-                        *reinterpret_cast<uint4*>(dst + c + 8 * q4) = w;
+                        for (int i = 0; i < 4; ++i)
+                            hh[i] = __floats2bfloat162_rn(__uint_as_float(raw[8 * g4 + 2 * i]) * inv, __uint_as_float(raw[8 * g4 + 2 * i + 1]) * inv);
+                        *reinterpret_cast<uint4*>(dst + c + 8 * g4) = w;
                     }
                 }
                 __syncwarp();
