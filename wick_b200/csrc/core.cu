@@ -112,6 +112,12 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const float
     sin_t[idx] = s;
 }
 
+// Two neighbouring elements at an even index.
+__device__ __forceinline__ float2 ld2(const float* p) { return *reinterpret_cast<const float2*>(p); }
+__device__ __forceinline__ float2 ld2(const __nv_bfloat16* p) { return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p)); }
+__device__ __forceinline__ void st2(float* p, float2 v) { *reinterpret_cast<float2*>(p) = v; }
+__device__ __forceinline__ void st2(__nv_bfloat16* p, float2 v) { *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v.x, v.y); }
+
 // ---- per-head norm + rotation + cache append --------------------------------
 // One warp per (token, head) vector of the fused projection output
 // qkv[token] = [q heads | k heads | v heads].  q goes to q_out, k and v go to the
@@ -138,15 +144,20 @@ __global__ void qk_norm_rope_append_kernel(
     const int half = hd >> 1;
     const int row_width = (n_heads + 2 * n_kv) * hd;
     // The projection output comes either as one array of T or as float32 partial
-    // sums [splits][tokens][row_width] that are added here, in index order.
+    // sums [splits][tokens][row_width] that are added here, in index order.  A lane
+    // takes two neighbouring elements at a time (i even).
     const int64_t base = (int64_t)t * row_width + (int64_t)h * hd;
-    auto val = [&](int i) -> float {
+    auto val2 = [&](int i) -> float2 {
         if (parts) {
-            float v = parts[base + i];
-            for (int sp = 1; sp < splits; ++sp) v += parts[sp * split_stride + base + i];
+            float2 v = *reinterpret_cast<const float2*>(parts + base + i);
+            for (int sp = 1; sp < splits; ++sp) {
+                const float2 u = *reinterpret_cast<const float2*>(parts + sp * split_stride + base + i);
+                v.x += u.x;
+                v.y += u.y;
+            }
             return v;
         }
-        return ld(qkv + base + i);
+        return ld2(qkv + base + i);
     };
 
     T* dst;
@@ -164,34 +175,52 @@ __global__ void qk_norm_rope_append_kernel(
         w = is_v ? nullptr : k_w;
         rotate = !is_v;
         if (is_v) {
-            for (int i = lane; i < hd; i += 32) st(dst + i, val(i));
+            for (int i = 2 * lane; i < hd; i += 64) st2(dst + i, val2(i));
             return;
         }
     }
+    // A lane holds, for i = 2 lane (+ 64, ...) below head_dim / 2, the elements i, i + 1 and
+    // their partners in the rotation, i + head_dim / 2 and i + 1 + head_dim / 2: everything
+    // it needs is loaded once.  head_dim <= 256: at most two such groups.
+    constexpr int MAXG = 2;
+    float2 xa[MAXG], xb[MAXG];
     float ss = 0.f;
-    for (int i = lane; i < hd; i += 32) {
-        const float v = val(i);
-        ss += v * v;
+#pragma unroll
+    for (int g = 0; g < MAXG; ++g) {
+        const int i = 2 * lane + 64 * g;
+        if (i < half) {
+            xa[g] = val2(i);
+            xb[g] = val2(i + half);
+            ss += xa[g].x * xa[g].x + xa[g].y * xa[g].y + xb[g].x * xb[g].x + xb[g].y * xb[g].y;
+        }
     }
     float scale = 1.f;
     if (w) {
         ss = warp_sum(ss);
         scale = 1.0f / sqrtf(ss / (float)hd + eps);
     }
-    for (int i = lane; i < half; i += 32) {
-        float a = val(i), b = val(i + half);
-        if (w) {
-            a = (a * scale) * w[i];
-            b = (b * scale) * w[i + half];
+#pragma unroll
+    for (int g = 0; g < MAXG; ++g) {
+        const int i = 2 * lane + 64 * g;
+        if (i < half) {
+            float2 a = xa[g], b = xb[g];
+            if (w) {
+                a.x = (a.x * scale) * w[i];
+                a.y = (a.y * scale) * w[i + 1];
+                b.x = (b.x * scale) * w[i + half];
+                b.y = (b.y * scale) * w[i + 1 + half];
+            }
+            if (rotate && cos_t) {
+                const float2 c = *reinterpret_cast<const float2*>(cos_t + (int64_t)t * half + i);
+                const float2 s = *reinterpret_cast<const float2*>(sin_t + (int64_t)t * half + i);
+                const float rax = a.x * c.x - b.x * s.x, rbx = b.x * c.x + a.x * s.x;
+                const float ray = a.y * c.y - b.y * s.y, rby = b.y * c.y + a.y * s.y;
+                a = make_float2(rax, ray);
+                b = make_float2(rbx, rby);
+            }
+            st2(dst + i, a);
+            st2(dst + i + half, b);
         }
-        if (rotate && cos_t) {
-            const float c = cos_t[(int64_t)t * half + i], s = sin_t[(int64_t)t * half + i];
-            const float ra = a * c - b * s, rb = b * c + a * s;
-            a = ra;
-            b = rb;
-        }
-        st(dst + i, a);
-        st(dst + i + half, b);
     }
 }
 
@@ -276,7 +305,7 @@ static int qk_norm_rope_append(const void* qkv, const float* parts, int splits, 
                                const float* k_w, float eps, const float* cos_t, const float* sin_t, void* q_out,
                                void* kv, const int* page_table, int table_width, const int* seq_of_token,
                                const int* positions, int write_kv, cudaStream_t s) {
-    WICK_REQUIRE(hd > 0 && hd % 2 == 0, "qk_norm_rope_append: head_dim %d must be even", hd);
+    WICK_REQUIRE(hd > 0 && hd % 4 == 0 && hd <= 256, "qk_norm_rope_append: head_dim %d must be a multiple of 4 up to 256", hd);
     WICK_REQUIRE(n_heads > 0 && n_kv > 0, "qk_norm_rope_append: bad head counts");
     if (n_tokens == 0) return 0;
     const int heads_total = n_heads + (write_kv ? 2 * n_kv : 0);
