@@ -50,10 +50,12 @@ constexpr int BK = 128;                                // keys of an inner step 
 constexpr int PANELS = HD / 64;                        // 64-column panels of a head row
 constexpr int PANEL_BYTES = 128 * 128;                 // 128 rows of 128 bytes
 constexpr int TILE_BYTES = PANELS * PANEL_BYTES;       // Q, or one block of keys or of values
-constexpr int NSLOT = 6;                               // key / value tiles in flight (3 blocks)
+constexpr int NSLOT = 6;                               // key / value tiles in flight: 2 per score buffer (the ring of
+                                                       // tiles and the ring of score buffers turn together)
 constexpr int SMEM_BYTES = TILE_BYTES + NSLOT * TILE_BYTES + 1024;
 constexpr int THREADS = 320;                           // warp 0: TMA, warp 1: MMA + tensor memory, warps 2-9: softmax
 constexpr int NBUF = 3;                                // score buffers
+static_assert(NSLOT == 2 * NBUF, "a tile slot is free when the scores (the product) of three blocks before are done");
 constexpr int HALF_K = BK / 2;                         // keys of a block that one softmax thread handles
 constexpr uint32_t TMEM_COLS = 512;                    // S0 | S1 | S2 | O; P (bfloat16 pairs) takes the place of the
 constexpr uint32_t COL_S = 0, COL_O = NBUF * BK;       // first 64 columns of the S buffer it was computed from
@@ -61,6 +63,12 @@ typedef __nv_bfloat16 bf16;
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Two barriers at once (their polls overlap).
+__device__ __forceinline__ bool mbar_wait2(uint64_t* a, uint32_t pa, uint64_t* b, uint32_t pb, volatile int* abort_flag, int* status, int code) {
+    const bool ra = mbar_try_wait(a, pa), rb = mbar_try_wait(b, pb);
+    if (ra && rb) return true;
+    return (ra || mbar_wait(a, pa, abort_flag, status, code)) && (rb || mbar_wait(b, pb, abort_flag, status, code));
 }
 __device__ __forceinline__ void tc_ld32_nowait(uint32_t taddr, uint32_t* r) {
     asm volatile(
@@ -142,7 +150,7 @@ attn_prompt_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_co
                       const int* __restrict__ page_table, int table_width, int n_tiles, int n_heads, int n_kv,
                       float scale, int* status) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ uint64_t q_full, full[NSLOT], empty[NSLOT];
+    __shared__ uint64_t q_full, full[NSLOT];
     __shared__ uint64_t s_full[NBUF], p_full[NBUF], pv_done[2], x_bar[4];   // pv_done: even blocks, odd blocks
     __shared__ bf16 mx_x[2][2][BQ];                            // the maxima the two halves of a row tell each other
     __shared__ uint32_t tmem_slot;
@@ -169,10 +177,7 @@ attn_prompt_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_co
     if (threadIdx.x == 0) {
         abort_flag = 0;
         mbar_init(&q_full, 1);
-        for (int s = 0; s < NSLOT; ++s) {
-            mbar_init(&full[s], 1);
-            mbar_init(&empty[s], 1);
-        }
+        for (int s = 0; s < NSLOT; ++s) mbar_init(&full[s], 1);
         for (int i = 0; i < NBUF; ++i) {
             mbar_init(&s_full[i], 1);
             // One arrival per softmax warp; a barrier per score buffer, since a warp may be up to
@@ -202,7 +207,13 @@ attn_prompt_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_co
             for (int pn = 0; pn < PANELS; ++pn) tma_load_2d(&q_map, &q_full, q_s + pn * PANEL_BYTES, head * HD + pn * 64, tok0 + q0);
             for (int i = 0; i < 2 * n_blk; ++i) {
                 const int slot = i % NSLOT, j = i >> 1, is_v = i & 1;
-                if (!mbar_wait(&empty[slot], ((i / NSLOT) & 1) ^ 1, &abort_flag, status, 7)) break;
+                // The slot held the keys (values) of block j - 3: free when that block's scores are
+                // computed (its P V product is complete), which is what s_full (pv_done) says.
+                if (j >= NBUF) {
+                    const int jp = j - NBUF;
+                    if (!(is_v ? mbar_wait(&pv_done[jp & 1], (jp >> 1) & 1, &abort_flag, status, 7)
+                               : mbar_wait(&s_full[jp % NBUF], (jp / NBUF) & 1, &abort_flag, status, 7))) break;
+                }
                 mbar_expect_tx(&full[slot], TILE_BYTES);
                 for (int w = 0; w < 2; ++w) {
                     const int idx = 2 * j + w;
@@ -233,24 +244,21 @@ attn_prompt_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_co
                     constexpr uint32_t off = (((int)ks >> 2) * PANEL_BYTES + ((int)ks & 3) * 32) >> 4;
                     mma_ss<((int)ks > 0)>(d, q_lo + off, k_lo + off, idesc_s);
                 });
-                tc_commit(&s_full[buf]);
-                tc_commit(&empty[slot]);                                     // the keys are read
+                tc_commit(&s_full[buf]);                                     // (also: the keys are read)
                 return true;
             };
             bool ok = mbar_wait(&q_full, 0, &abort_flag, status, 7);
             for (int j = 0; j < NBUF && j < n_blk && ok; ++j) ok = issue_s(j);
             for (int j = 0; j < n_blk && ok; ++j) {
                 const int i = 2 * j + 1, slot = i % NSLOT;
-                ok = ok && mbar_wait(&p_full[j % NBUF], (j / NBUF) & 1, &abort_flag, status, 7);
-                ok = ok && mbar_wait(&full[slot], (i / NSLOT) & 1, &abort_flag, status, 7);
+                ok = ok && mbar_wait2(&p_full[j % NBUF], (j / NBUF) & 1, &full[slot], (i / NSLOT) & 1, &abort_flag, status, 7);
                 if (!ok) break;
                 tc_fence_after();
                 const uint32_t v_lo = v_lo0 + slot * (TILE_BYTES >> 4), d = tmem + COL_O, pa = tmem + COL_S + (j % NBUF) * BK;
                 if (j > 0) mma_ts<1>(d, pa, v_lo, idesc_o);
                 else mma_ts<0>(d, pa, v_lo, idesc_o);
                 static_for<1, BK / 16>([&](auto ks) { mma_ts<1>(d, pa + (int)ks * 8, v_lo + (int)ks * (2048 >> 4), idesc_o); });
-                tc_commit(&pv_done[j & 1]);
-                tc_commit(&empty[slot]);                                     // the values are read
+                tc_commit(&pv_done[j & 1]);                                  // (also: the values are read)
                 if (j + NBUF < n_blk) {
                     // the scores of block j + 3 go where this block's P lies: only when it has been read
                     ok = mbar_wait(&pv_done[j & 1], (j >> 1) & 1, &abort_flag, status, 7) && issue_s(j + NBUF);
