@@ -27,6 +27,25 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
 }
 
 // ---- RMSNorm ---------------------------------------------------------------
+// Two kernels compute it: one block per row (few rows: a decode step) and one warp
+// per row (many rows: a prompt).  They give the same bits: the warp plays every
+// thread of the block in turn, and the operations below are spelled out so that the
+// compiler contracts nothing differently in the two.
+__device__ __forceinline__ float sumsq4(float ss, float4 v) {
+    return __fadd_rn(ss, __fadd_rn(__fadd_rn(__fadd_rn(__fmul_rn(v.x, v.x), __fmul_rn(v.y, v.y)), __fmul_rn(v.z, v.z)), __fmul_rn(v.w, v.w)));
+}
+__device__ __forceinline__ float normed(float v, float scale, float g) { return __fmul_rn(__fmul_rn(v, scale), g); }
+// Four neighbouring outputs at an index that is a multiple of 4.
+__device__ __forceinline__ void st4(float* p, float a, float b, float c, float d) { *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d); }
+__device__ __forceinline__ void st4(__nv_bfloat16* p, float a, float b, float c, float d) {
+    uint2 u;
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    u.x = *reinterpret_cast<uint32_t*>(&lo);
+    u.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = u;
+}
+__device__ __forceinline__ float rms_scale(float ss, int width, float eps) { return 1.0f / sqrtf(__fadd_rn(__fdiv_rn(ss, (float)width), eps)); }
+
 // One block per output row i.  Source row r = rows ? rows[i] : i.  If delta is
 // given, x[r] += delta[0][r] + delta[1][r] + ... (index order) and is written
 // back before it is normalised.
@@ -57,7 +76,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
                 *reinterpret_cast<float4*>(xr + j) = v;
             }
             *reinterpret_cast<float4*>(row + j) = v;
-            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            ss = sumsq4(ss, v);
         }
     } else {
         for (int j = threadIdx.x; j < width; j += blockDim.x) {
@@ -71,20 +90,95 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
         }
     }
     ss = block_sum(ss, red);
-    const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+    const float scale = rms_scale(ss, width, eps);
     TOut* o = out + (int64_t)i * width;
     if ((width & 3) == 0) {
         for (int j = threadIdx.x * 4; j < width; j += blockDim.x * 4) {
             const float4 v = *reinterpret_cast<const float4*>(row + j);
             const float4 g = *reinterpret_cast<const float4*>(w + j);
-            st(o + j, (v.x * scale) * g.x);
-            st(o + j + 1, (v.y * scale) * g.y);
-            st(o + j + 2, (v.z * scale) * g.z);
-            st(o + j + 3, (v.w * scale) * g.w);
+            st(o + j, normed(v.x, scale, g.x));
+            st(o + j + 1, normed(v.y, scale, g.y));
+            st(o + j + 2, normed(v.z, scale, g.z));
+            st(o + j + 3, normed(v.w, scale, g.w));
         }
     } else {
         for (int j = threadIdx.x; j < width; j += blockDim.x) st(o + j, (row[j] * scale) * w[j]);
     }
+}
+
+// One warp per output row, for rows that are a multiple of 4 wide and at most 4096:
+// the row stays in registers, nothing is synchronised but the warp.  VT: the threads the
+// block kernel would run for this width; lane l plays its threads l, l + 32, ... so that
+// the sum of squares is added up in exactly that kernel's order.
+template <typename TOut, int VT>
+__global__ void __launch_bounds__(128) rmsnorm_rows_kernel(float* __restrict__ x, const float* __restrict__ delta, int splits,
+                                                           int64_t split_stride, const float* __restrict__ w, float eps,
+                                                           const int* __restrict__ rows, TOut* __restrict__ out, int n_out,
+                                                           int width) {
+    pdl_trigger();
+    pdl_wait();
+    x = fresh(x);
+    delta = fresh(delta);
+    constexpr int NW = VT / 32;                         // warps of the block kernel
+    constexpr int KMAX = 4096 / 4 / VT > 0 ? 4096 / 4 / VT : 1;   // float4s per thread of the block kernel (widths up to 4096)
+    const int lane = threadIdx.x & 31;
+    const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (i >= n_out) return;
+    const int64_t r = rows ? rows[i] : i;
+    float* xr = x + r * width;
+    float4 v[NW][KMAX];
+#pragma unroll
+    for (int wv = 0; wv < NW; ++wv)
+#pragma unroll
+        for (int k = 0; k < KMAX; ++k) {
+            const int j = ((wv * 32 + lane) + k * VT) * 4;
+            v[wv][k] = j < width ? *reinterpret_cast<const float4*>(xr + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    if (delta) {
+        for (int s = 0; s < splits; ++s) {
+#pragma unroll
+            for (int wv = 0; wv < NW; ++wv)
+#pragma unroll
+                for (int k = 0; k < KMAX; ++k) {
+                    const int j = ((wv * 32 + lane) + k * VT) * 4;
+                    if (j < width) {
+                        const float4 d = *reinterpret_cast<const float4*>(delta + s * split_stride + r * width + j);
+                        v[wv][k].x += d.x; v[wv][k].y += d.y; v[wv][k].z += d.z; v[wv][k].w += d.w;
+                    }
+                }
+        }
+#pragma unroll
+        for (int wv = 0; wv < NW; ++wv)
+#pragma unroll
+            for (int k = 0; k < KMAX; ++k) {
+                const int j = ((wv * 32 + lane) + k * VT) * 4;
+                if (j < width) *reinterpret_cast<float4*>(xr + j) = v[wv][k];
+            }
+    }
+    // the block kernel's sum: per thread over k, per warp by the butterfly, then over the warps by the butterfly
+    float total_in = 0.f;
+#pragma unroll
+    for (int wv = 0; wv < NW; ++wv) {
+        float ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < KMAX; ++k)
+            if (((wv * 32 + lane) + k * VT) * 4 < width) ss = sumsq4(ss, v[wv][k]);
+        ss = warp_sum(ss);
+        if (lane == wv) total_in = ss;
+    }
+    const float scale = rms_scale(warp_sum(total_in), width, eps);
+    TOut* o = out + (int64_t)i * width;
+#pragma unroll
+    for (int wv = 0; wv < NW; ++wv)
+#pragma unroll
+        for (int k = 0; k < KMAX; ++k) {
+            const int j = ((wv * 32 + lane) + k * VT) * 4;
+            if (j < width) {
+                const float4 g = *reinterpret_cast<const float4*>(w + j);
+                const float4 q = v[wv][k];
+                st4(o + j, normed(q.x, scale, g.x), normed(q.y, scale, g.y), normed(q.z, scale, g.z), normed(q.w, scale, g.w));
+            }
+        }
 }
 
 // x[r] += sum of delta for every row (no norm): resolves a pending residual.
@@ -256,6 +350,15 @@ int rmsnorm(float* x, const float* delta, int splits, int64_t n_rows_x, const fl
         raised = true;
     }
     const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    if (n_out >= 32 && width % 4 == 0 && width <= 4096) {
+        // many rows: a warp per row (same bits as the block per row)
+        const dim3 grid(ceil_div(n_out, 4)), block(128);
+        const int64_t stride = n_rows_x * width;
+        if (threads == 512) WICK_CUDA(launch(rmsnorm_rows_kernel<TOut, 512>, grid, block, 0, s, x, delta, splits, stride, w, eps, rows, (TOut*)out, n_out, width));
+        else if (threads == 256) WICK_CUDA(launch(rmsnorm_rows_kernel<TOut, 256>, grid, block, 0, s, x, delta, splits, stride, w, eps, rows, (TOut*)out, n_out, width));
+        else WICK_CUDA(launch(rmsnorm_rows_kernel<TOut, 128>, grid, block, 0, s, x, delta, splits, stride, w, eps, rows, (TOut*)out, n_out, width));
+        return check_launch("rmsnorm");
+    }
     WICK_CUDA(launch(rmsnorm_kernel<TOut>, dim3(n_out), dim3(threads), smem, s, x, delta, splits, n_rows_x * width, w,
                      eps, rows, (TOut*)out, width));
     return check_launch("rmsnorm");
