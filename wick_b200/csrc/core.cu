@@ -215,8 +215,10 @@ __device__ __forceinline__ void st2(__nv_bfloat16* p, float2 v) { *reinterpret_c
 // ---- per-head norm + rotation + cache append --------------------------------
 // One warp per (token, head) vector of the fused projection output
 // qkv[token] = [q heads | k heads | v heads].  q goes to q_out, k and v go to the
-// token's place in its sequence's cache page.
-template <typename T>
+// token's place in its sequence's cache page.  A warp takes HB vectors in a row and
+// issues the loads of all of them before it uses the first (a prompt's kernel is
+// bound by how many loads are in flight, not by arithmetic).
+template <typename T, int HB>
 __global__ void qk_norm_rope_append_kernel(
     const T* __restrict__ qkv, const float* __restrict__ parts, int splits, int64_t split_stride,
     int n_tokens, int n_heads, int n_kv, int hd,
@@ -232,88 +234,96 @@ __global__ void qk_norm_rope_append_kernel(
     sin_t = fresh(sin_t);
     const int lane = threadIdx.x & 31;
     const int heads_total = n_heads + (write_kv ? 2 * n_kv : 0);
-    const int64_t item = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (item >= (int64_t)n_tokens * heads_total) return;
-    const int t = item / heads_total, h = item % heads_total;
+    // grid: (tokens, groups of heads): no division to find a vector's token and head
+    const int t = blockIdx.x;
+    const int h0 = (blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5)) * HB;
+    if (h0 >= heads_total) return;
     const int half = hd >> 1;
     const int row_width = (n_heads + 2 * n_kv) * hd;
-    // The projection output comes either as one array of T or as float32 partial
-    // sums [splits][tokens][row_width] that are added here, in index order.  A lane
-    // takes two neighbouring elements at a time (i even).
-    const int64_t base = (int64_t)t * row_width + (int64_t)h * hd;
-    auto val2 = [&](int i) -> float2 {
-        if (parts) {
-            float2 v = *reinterpret_cast<const float2*>(parts + base + i);
-            for (int sp = 1; sp < splits; ++sp) {
-                const float2 u = *reinterpret_cast<const float2*>(parts + sp * split_stride + base + i);
-                v.x += u.x;
-                v.y += u.y;
-            }
-            return v;
-        }
-        return ld2(qkv + base + i);
-    };
-
-    T* dst;
-    const float* w = nullptr;
-    bool rotate = true;
-    if (h < n_heads) {
-        dst = q_out + ((int64_t)t * n_heads + h) * hd;
-        w = q_w;
-    } else {
-        const int is_v = h >= n_heads + n_kv;
-        const int kh = h - n_heads - (is_v ? n_kv : 0);
-        const int pos = positions[t];
-        const int page = page_table[(int64_t)seq_of_token[t] * table_width + pos / kPage];
-        dst = kv + ((((int64_t)page * 2 + is_v) * n_kv + kh) * kPage + (pos % kPage)) * hd;
-        w = is_v ? nullptr : k_w;
-        rotate = !is_v;
-        if (is_v) {
-            for (int i = 2 * lane; i < hd; i += 64) st2(dst + i, val2(i));
-            return;
-        }
-    }
     // A lane holds, for i = 2 lane (+ 64, ...) below head_dim / 2, the elements i, i + 1 and
     // their partners in the rotation, i + head_dim / 2 and i + 1 + head_dim / 2: everything
     // it needs is loaded once.  head_dim <= 256: at most two such groups.
     constexpr int MAXG = 2;
-    float2 xa[MAXG], xb[MAXG];
-    float ss = 0.f;
+    float2 xa[HB][MAXG], xb[HB][MAXG];
 #pragma unroll
-    for (int g = 0; g < MAXG; ++g) {
-        const int i = 2 * lane + 64 * g;
-        if (i < half) {
-            xa[g] = val2(i);
-            xb[g] = val2(i + half);
-            ss += xa[g].x * xa[g].x + xa[g].y * xa[g].y + xb[g].x * xb[g].x + xb[g].y * xb[g].y;
+    for (int u = 0; u < HB; ++u) {
+        const int h = h0 + u;
+        if (h >= heads_total) break;
+        // The projection output comes either as one array of T or as float32 partial
+        // sums [splits][tokens][row_width] that are added here, in index order.
+        const int64_t base = (int64_t)t * row_width + (int64_t)h * hd;
+        auto val2 = [&](int i) -> float2 {
+            if (parts) {
+                float2 v = *reinterpret_cast<const float2*>(parts + base + i);
+                for (int sp = 1; sp < splits; ++sp) {
+                    const float2 d = *reinterpret_cast<const float2*>(parts + sp * split_stride + base + i);
+                    v.x += d.x;
+                    v.y += d.y;
+                }
+                return v;
+            }
+            return ld2(qkv + base + i);
+        };
+#pragma unroll
+        for (int g = 0; g < MAXG; ++g) {
+            const int i = 2 * lane + 64 * g;
+            if (i < half) {
+                xa[u][g] = val2(i);
+                xb[u][g] = val2(i + half);
+            }
         }
     }
-    float scale = 1.f;
-    if (w) {
-        ss = warp_sum(ss);
-        scale = 1.0f / sqrtf(ss / (float)hd + eps);
-    }
 #pragma unroll
-    for (int g = 0; g < MAXG; ++g) {
-        const int i = 2 * lane + 64 * g;
-        if (i < half) {
-            float2 a = xa[g], b = xb[g];
-            if (w) {
-                a.x = (a.x * scale) * w[i];
-                a.y = (a.y * scale) * w[i + 1];
-                b.x = (b.x * scale) * w[i + half];
-                b.y = (b.y * scale) * w[i + 1 + half];
+    for (int u = 0; u < HB; ++u) {
+        const int h = h0 + u;
+        if (h >= heads_total) break;
+        T* dst;
+        const float* w = nullptr;
+        bool rotate = true;
+        if (h < n_heads) {
+            dst = q_out + ((int64_t)t * n_heads + h) * hd;
+            w = q_w;
+        } else {
+            const int is_v = h >= n_heads + n_kv;
+            const int kh = h - n_heads - (is_v ? n_kv : 0);
+            const int pos = positions[t];
+            const int page = page_table[(int64_t)seq_of_token[t] * table_width + pos / kPage];
+            dst = kv + ((((int64_t)page * 2 + is_v) * n_kv + kh) * kPage + (pos % kPage)) * hd;
+            w = is_v ? nullptr : k_w;
+            rotate = !is_v;                                    // the value goes into the cache as it is
+        }
+        float scale = 1.f;
+        if (w) {
+            float ss = 0.f;
+#pragma unroll
+            for (int g = 0; g < MAXG; ++g)
+                if (2 * lane + 64 * g < half)
+                    ss += xa[u][g].x * xa[u][g].x + xa[u][g].y * xa[u][g].y + xb[u][g].x * xb[u][g].x + xb[u][g].y * xb[u][g].y;
+            ss = warp_sum(ss);
+            scale = 1.0f / sqrtf(ss / (float)hd + eps);
+        }
+#pragma unroll
+        for (int g = 0; g < MAXG; ++g) {
+            const int i = 2 * lane + 64 * g;
+            if (i < half) {
+                float2 a = xa[u][g], b = xb[u][g];
+                if (w) {
+                    a.x = (a.x * scale) * w[i];
+                    a.y = (a.y * scale) * w[i + 1];
+                    b.x = (b.x * scale) * w[i + half];
+                    b.y = (b.y * scale) * w[i + 1 + half];
+                }
+                if (rotate && cos_t) {
+                    const float2 c = *reinterpret_cast<const float2*>(cos_t + (int64_t)t * half + i);
+                    const float2 sn = *reinterpret_cast<const float2*>(sin_t + (int64_t)t * half + i);
+                    const float rax = a.x * c.x - b.x * sn.x, rbx = b.x * c.x + a.x * sn.x;
+                    const float ray = a.y * c.y - b.y * sn.y, rby = b.y * c.y + a.y * sn.y;
+                    a = make_float2(rax, ray);
+                    b = make_float2(rbx, rby);
+                }
+                st2(dst + i, a);
+                st2(dst + i + half, b);
             }
-            if (rotate && cos_t) {
-                const float2 c = *reinterpret_cast<const float2*>(cos_t + (int64_t)t * half + i);
-                const float2 s = *reinterpret_cast<const float2*>(sin_t + (int64_t)t * half + i);
-                const float rax = a.x * c.x - b.x * s.x, rbx = b.x * c.x + a.x * s.x;
-                const float ray = a.y * c.y - b.y * s.y, rby = b.y * c.y + a.y * s.y;
-                a = make_float2(rax, ray);
-                b = make_float2(rbx, rby);
-            }
-            st2(dst + i, a);
-            st2(dst + i + half, b);
         }
     }
 }
@@ -413,10 +423,17 @@ static int qk_norm_rope_append(const void* qkv, const float* parts, int splits, 
     if (n_tokens == 0) return 0;
     const int heads_total = n_heads + (write_kv ? 2 * n_kv : 0);
     const int warps = 4;
-    WICK_CUDA(launch(qk_norm_rope_append_kernel<T>, dim3(ceil_div((int64_t)n_tokens * heads_total, warps)),
-                     dim3(warps * 32), 0, s, (const T*)qkv, parts, splits,
-                     (int64_t)n_tokens * (n_heads + 2 * n_kv) * hd, n_tokens, n_heads, n_kv, hd, q_w, k_w, eps, cos_t,
-                     sin_t, (T*)q_out, (T*)kv, page_table, table_width, seq_of_token, positions, write_kv));
+    const int64_t stride = (int64_t)n_tokens * (n_heads + 2 * n_kv) * hd;
+    WICK_REQUIRE(heads_total <= 65535 * warps, "qk_norm_rope_append: %d heads is beyond the grid limit", heads_total);
+    if ((int64_t)n_tokens * heads_total >= 8192) {            // a prompt: two vectors per warp
+        WICK_CUDA(launch(qk_norm_rope_append_kernel<T, 2>, dim3(n_tokens, ceil_div(heads_total, warps * 2)), dim3(warps * 32), 0, s,
+                         (const T*)qkv, parts, splits, stride, n_tokens, n_heads, n_kv, hd, q_w, k_w, eps, cos_t, sin_t, (T*)q_out,
+                         (T*)kv, page_table, table_width, seq_of_token, positions, write_kv));
+    } else {
+        WICK_CUDA(launch(qk_norm_rope_append_kernel<T, 1>, dim3(n_tokens, ceil_div(heads_total, warps)), dim3(warps * 32), 0, s,
+                         (const T*)qkv, parts, splits, stride, n_tokens, n_heads, n_kv, hd, q_w, k_w, eps, cos_t, sin_t, (T*)q_out,
+                         (T*)kv, page_table, table_width, seq_of_token, positions, write_kv));
+    }
     return check_launch("qk_norm_rope_append");
 }
 
