@@ -11,7 +11,9 @@ import torch
 
 from plain import qwen3_plain as P
 
-FIXTURE = os.environ.get("WICK_REFERENCE_FIXTURE", "/root/reference/tests/fixtures/tiny/qwen3-qknorm-f32")
+# wick's source tree is looked for beside this repository unless the variable names it.
+_BESIDE = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference")
+FIXTURE = os.environ.get("WICK_REFERENCE_FIXTURE", os.path.join(_BESIDE, "tests", "fixtures", "tiny", "qwen3-qknorm-f32"))
 needs_fixture = pytest.mark.skipif(not os.path.isdir(FIXTURE), reason="wick's fixture is not on this machine")
 
 
