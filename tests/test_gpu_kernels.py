@@ -56,6 +56,25 @@ def test_rmsnorm_plain_with_delta_and_with_rows(ops, out_dtype, width):
     assert torch.equal(xd.cpu()[1], x[1]), "rows that were not asked for stay untouched"
 
 
+@pytest.mark.parametrize("out_dtype", DTYPES)
+@pytest.mark.parametrize("width", [72, 1000, 4096])
+def test_rmsnorm_of_many_rows_gives_the_bits_of_few_rows(ops, out_dtype, width):
+    """600 rows take the kernel with a warp per row, 9 rows the one with a block
+    per row: a token's norm must not depend on how many others share its step."""
+    torch.manual_seed(width + 1)
+    n = 600
+    x, w, delta = torch.randn(n, width) * 3, 1 + 0.1 * torch.randn(width), torch.randn(2, n, width)
+    xs = x + (delta[0] + delta[1])
+    ref = P.rms_norm(xs, w, 1e-5)
+    xd = dev(x.clone())
+    got = ops.rmsnorm(xd, dev(w), 1e-5, out_dtype, delta=dev(delta))
+    assert (got.float().cpu() - ref).abs().max() < tol(out_dtype, ref.abs().max())
+    assert torch.allclose(xd.cpu(), xs, atol=1e-6)
+    pick = [0, 1, 77, 300, 598, 599, 5, 6, 7]
+    few = ops.rmsnorm(dev(x[pick].clone()), dev(w), 1e-5, out_dtype, delta=dev(delta[:, pick].contiguous()))
+    assert torch.equal(few.cpu(), got.cpu()[pick])
+
+
 def test_add_delta(ops):
     x, d = torch.randn(5, 33), torch.randn(2, 5, 33)
     got = ops.add_delta(dev(x.clone()), dev(d))

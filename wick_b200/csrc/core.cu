@@ -360,8 +360,10 @@ int rmsnorm(float* x, const float* delta, int splits, int64_t n_rows_x, const fl
         raised = true;
     }
     const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
-    if (n_out >= 32 && width % 4 == 0 && width <= 4096) {
-        // many rows: a warp per row (same bits as the block per row)
+    if (n_out >= 512 && width % 4 == 0 && width <= 4096) {
+        // Enough rows to give every SM its warps: a warp per row (same bits as the block per row).
+        // With fewer rows (a decode step of 64 sequences) a warp per row leaves most of the part
+        // idle and each warp walks its row's partial sums alone: the block per row is 3x faster there.
         const dim3 grid(ceil_div(n_out, 4)), block(128);
         const int64_t stride = n_rows_x * width;
         if (threads == 512) WICK_CUDA(launch(rmsnorm_rows_kernel<TOut, 512>, grid, block, 0, s, x, delta, splits, stride, w, eps, rows, (TOut*)out, n_out, width));
