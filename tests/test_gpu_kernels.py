@@ -418,6 +418,41 @@ def test_top_k_sorted_with_index_tie_break(ops, vocab, k):
         assert torch.equal(vals[r], x[r][order])
 
 
+@pytest.mark.parametrize("k, temperature, min_p, top_p", [(40, 0.7, 0.0, 0.9), (20, 1.1, 0.05, 0.8), (1, 0.5, 0.0, 0.9),
+                                                            (333, 1.0, 0.0, 1.0), (1024, 0.3, 0.2, 0.5), (7, 2.0, 0.9, 1.0)])
+def test_pick_from_sorted_candidates(ops, k, temperature, min_p, top_p):
+    """The cuts and the draw on the device against their plain form on the host, from
+    the same sorted candidates and the same uniform numbers.  (The two exponentials may
+    differ in the last bit: a draw that falls on a boundary may then take the neighbour.)"""
+    from wick_b200.sampling.sampler import SamplerConfig, pick_from_sorted
+
+    class Fixed:
+        def __init__(self, u):
+            self.u = u
+
+        def next_f32(self):
+            return self.u
+
+    torch.manual_seed(k)
+    rows = 300
+    logits = torch.randn(rows, 5003) * 3
+    logits[5, :] = 0.25                                           # all candidates equal
+    vals, idx = ops.top_k(dev(logits), k)
+    u = torch.rand(rows)
+    u[0], u[1] = 0.0, 1.0 - 2.0 ** -24                            # the ends of the generator's range
+    got = ops.pick_sorted(vals, idx, dev(u), temperature, min_p, top_p).tolist()
+    cfg = SamplerConfig(temperature=temperature, top_k=k, top_p=top_p, min_p=min_p)
+    v, ix = vals.cpu().numpy(), idx.cpu().numpy()
+    off = 0
+    for r in range(rows):
+        want = pick_from_sorted(v[r], ix[r], cfg, Fixed(float(u[r])))
+        if got[r] != want:
+            off += 1
+            place = {int(t): i for i, t in enumerate(ix[r])}
+            assert abs(place[got[r]] - place[want]) == 1, (r, got[r], want)
+    assert off <= 1
+
+
 def test_repetition_penalty(ops):
     x = torch.tensor([[2.0, -2.0, 4.0, 1.0], [1.0, 1.0, -1.0, 0.0]])
     got = ops.repetition_penalty(dev(x.clone()), [[0, 1, 1, 0], [2, 9]], 2.0).cpu()

@@ -217,9 +217,69 @@ top_k_kernel(const float* __restrict__ logits, float* __restrict__ vals, int* __
     }
 }
 
+// One token per row from k candidates sorted by logit (descending): probabilities
+// exp((l - max) / T) normalised by their sum, the min-p cut, the top-p cut and one draw
+// r = u * (sum of what is left) walked down the candidates (wick src/sampler.rs:95-125).
+// One thread per row does the sums one after the other in float32, as the reference's
+// iterator sums do (k <= 1024 on the usual path; nothing here is worth more threads).
+// probs: scratch [rows, k].
+__global__ void pick_sorted_kernel(const float* __restrict__ vals, const int* __restrict__ idxs, const float* __restrict__ uniforms,
+                                   float* __restrict__ probs, int* __restrict__ out, int rows, int k, float temperature,
+                                   float min_p, float top_p) {
+    pdl_trigger();
+    pdl_wait();
+    vals = fresh(vals);
+    idxs = fresh(idxs);
+    const int row = blockIdx.x * blockDim.x + threadIdx.x;
+    if (row >= rows) return;
+    const float* v = vals + (int64_t)row * k;
+    const int* ix = idxs + (int64_t)row * k;
+    float* p = probs + (int64_t)row * k;
+    const float top = v[0];
+    float total = 0.f;
+    for (int i = 0; i < k; ++i) {
+        p[i] = expf(__fdiv_rn(__fsub_rn(v[i], top), temperature));
+        total = __fadd_rn(total, p[i]);
+    }
+    for (int i = 0; i < k; ++i) p[i] = __fdiv_rn(p[i], total);
+    int keep = k;
+    if (min_p > 0.f) {
+        const float floor_p = __fmul_rn(p[0], min_p);
+        for (int i = 0; i < k; ++i)
+            if (p[i] < floor_p) { keep = i > 1 ? i : 1; break; }
+    }
+    if (top_p < 1.f) {
+        float acc = 0.f;
+        for (int i = 0; i < keep; ++i) {
+            acc = __fadd_rn(acc, p[i]);
+            if (acc >= top_p) { keep = i + 1; break; }
+        }
+    }
+    float tot = 0.f;
+    for (int i = 0; i < keep; ++i) tot = __fadd_rn(tot, p[i]);
+    float r = __fmul_rn(uniforms[row], tot);
+    int pick = ix[keep - 1];
+    for (int i = 0; i < keep; ++i) {
+        r = __fsub_rn(r, p[i]);
+        if (r <= 0.f) { pick = ix[i]; break; }
+    }
+    out[row] = pick;
+}
+
 }  // namespace wick
 
 using namespace wick;
+
+// vals, idxs: [rows, k] candidates sorted by value (descending); uniforms: [rows] in [0, 1);
+// probs: float32 scratch [rows, k]; out: int32 [rows].
+WICK_API int wick_pick_sorted(const float* vals, const int* idxs, const float* uniforms, float* probs, int* out, int rows, int k,
+                              float temperature, float min_p, float top_p, void* s) {
+    WICK_REQUIRE(rows >= 0 && k >= 1 && temperature > 0.f, "pick_sorted: bad arguments");
+    if (rows == 0) return 0;
+    WICK_CUDA(launch(pick_sorted_kernel, dim3(ceil_div(rows, 32)), dim3(32), 0, (cudaStream_t)s, vals, idxs, uniforms, probs, out,
+                     rows, k, temperature, min_p, top_p));
+    return check_launch("pick_sorted");
+}
 
 WICK_API int wick_argmax(const float* logits, int* out, int rows, int vocab, void* s) {
     WICK_REQUIRE(vocab > 0 && rows >= 0, "argmax: bad sizes");

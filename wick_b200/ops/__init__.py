@@ -495,6 +495,24 @@ def top_k(logits: torch.Tensor, k: int) -> Tuple[torch.Tensor, torch.Tensor]:
     return vals, idx
 
 
+def pick_sorted(vals: torch.Tensor, idx: torch.Tensor, uniforms: torch.Tensor, temperature: float, min_p: float,
+                top_p: float) -> torch.Tensor:
+    """One token per row from candidates sorted by logit (descending): the
+    probabilities at ``temperature``, the min-p and top-p cuts and the draw with
+    the row's uniform number, as ``sampling.sampler.pick_from_sorted`` does them
+    on the host (int32 [rows])."""
+    _cuda("vals", vals, torch.float32)
+    rows, k = vals.shape
+    _cuda("idx", idx, torch.int32, (rows, k))
+    _cuda("uniforms", uniforms, torch.float32, (rows,))
+    _need(temperature > 0.0, "pick_sorted needs a temperature above 0")
+    probs = torch.empty_like(vals)
+    out = torch.empty(rows, dtype=torch.int32, device=vals.device)
+    _core().call("wick_pick_sorted", "pppppiifffp", _p(vals), _p(idx), _p(uniforms), _p(probs), _p(out), rows, k,
+                 float(temperature), float(min_p), float(top_p), _stream())
+    return out
+
+
 def repetition_penalty(logits: torch.Tensor, histories, penalty: float) -> torch.Tensor:
     """In place: every distinct token of histories[row] has its logit divided by
     ``penalty`` if positive, multiplied otherwise."""

@@ -10,10 +10,11 @@ The generator is xoshiro256** seeded through splitmix64 (``:29-61``); every
 sequence gets a generator of its own from the seed, so a sequence samples the
 same tokens alone or in a batch.
 
-Device side: the argmax, the top-k selection and (without candidate cuts) the
-whole draw are CUDA kernels; with candidate cuts the k sorted candidates (at
-most 1024 per row) come to the host, where min-p, top-p and the draw are done in
-float32 exactly as above.
+Device side: the argmax, the top-k selection (up to 1024 candidates per row),
+the cuts and the draw are CUDA kernels; only each sequence's uniform number comes
+from the host, from that sequence's generator.  :func:`pick_from_sorted` is the
+plain form of the cuts and the draw (float32 on the host, one operation at a
+time) that the tests hold the kernel against.
 """
 from __future__ import annotations
 
@@ -140,10 +141,9 @@ class Sampler:
             return ops.sample_temperature(logits, cfg.temperature, u.to(logits.device)).tolist()
         if k <= self.DEVICE_TOP_K:
             vals, idx = ops.top_k(logits, k)
-            vals, idx = vals.cpu().numpy(), idx.cpu().numpy()
         else:
-            # All candidates with cuts: rare; sort on the host.
-            host = logits.cpu().numpy()
-            order = np.argsort(-host, axis=1, kind="stable")[:, :k]
-            vals, idx = np.take_along_axis(host, order, axis=1), order
-        return [pick_from_sorted(vals[i], idx[i], cfg, self.rngs[s]) for i, s in enumerate(seq_ids)]
+            # More candidates than the selection kernel takes (rare): a library sort, ties by index.
+            vals, order = torch.sort(logits, dim=1, descending=True, stable=True)
+            vals, idx = vals[:, :k].contiguous(), order[:, :k].to(torch.int32).contiguous()
+        u = torch.tensor([self.rngs[s].next_f32() for s in seq_ids], dtype=torch.float32)
+        return ops.pick_sorted(vals, idx, u.to(logits.device), cfg.temperature, cfg.min_p, cfg.top_p).tolist()
