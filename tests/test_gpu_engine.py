@@ -268,15 +268,17 @@ def test_model_with_random_weights_drawn_on_the_device():
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_real_layer_widths_of_qwen3_8b(dtype):
+@pytest.mark.parametrize("lens", [(150, 37), (300, 25)])
+def test_real_layer_widths_of_qwen3_8b(dtype, lens):
     """One layer at the real widths (config R): a prompt whole, a second prompt in
     the same batch, then decoded tokens — so that the kernels run with their real
     tile counts, splits and strides.  float32 must match the plain implementation
-    to 1e-4 here too."""
+    to 1e-4 here too.  (313 tokens in a step: the matrix products on pairs of thread
+    blocks, the narrow ones with their inner dimension cut into runs.)"""
     name = "R"
     eng = make_engine(name, dtype, max_tokens=1024)
     poison_all(eng)
-    seqs = [random_tokens(vocab_of(name), n, 900 + n) for n in (150, 37)]
+    seqs = [random_tokens(vocab_of(name), n, 900 + n) for n in lens]
     refs = [plain_logits(name, s) for s in seqs]
     slots = [eng.open_seq() for _ in seqs]
     heads = [len(s) - 6 for s in seqs]

@@ -516,10 +516,12 @@ def test_gemm_tensor_core_both_ways_round(t, n, k, gated):
 
 
 @pytest.mark.parametrize("t, n, k, gated", [(256, 256, 64, False), (257, 100, 72, True), (700, 520, 200, False),
-                                            (1000, 333, 328, True), (2100, 1536, 1024, False)])
+                                            (1000, 333, 328, True), (2100, 1536, 1024, False),
+                                            (512, 1024, 4096, False), (300, 300, 8264, False)])
 def test_gemm_tensor_core_single_blocks_and_pairs(monkeypatch, t, n, k, gated):
     """From 256 tokens on two thread blocks share a 256 x 256 tile; the kernel for
-    single blocks takes the same sizes.  Both against a float64 product."""
+    single blocks takes the same sizes.  Both against a float64 product.  (The last two
+    sizes make few tiles with a long inner dimension: it is cut into 2 and 4 runs.)"""
     from wick_b200.ops import gemm_tc as G
     torch.manual_seed(t + n + k)
     x = torch.randn(t, k).bfloat16()
@@ -539,9 +541,19 @@ def test_gemm_tensor_core_single_blocks_and_pairs(monkeypatch, t, n, k, gated):
         monkeypatch.setattr(G, "PAIR_MIN", 256)
         res = torch.randn(t, n)
         acc = dev(res.clone())
-        assert plan.forward_add(dev(x), acc)
-        G.check_status()
-        assert torch.equal(acc, dev(res) + plan.forward(dev(x), torch.float32))
+        runs = plan.prompt_splits(t)
+        assert runs == {(512, 1024, 4096): 2, (300, 300, 8264): 4}.get((t, n, k), 1)
+        if runs == 1:
+            assert plan.forward_add(dev(x), acc)
+            G.check_status()
+            assert torch.equal(acc, dev(res) + plan.forward(dev(x), torch.float32))
+        else:
+            assert not plan.forward_add(dev(x), acc), "few tiles: partial sums over runs of the inner dimension"
+            parts = plan.forward_delta(dev(x))
+            G.check_status()
+            assert parts.shape == (runs, t, n)
+            assert (parts.sum(0).cpu() - ref).abs().max() < 2e-4 * max(1.0, ref.abs().max())
+            assert torch.equal(parts, plan.forward_delta(dev(x))), "the same bits in every run"
         assert not plan.forward_add(dev(x[:100]), dev(res[:100].clone())), "few tokens: the caller adds"
 
 

@@ -15,6 +15,10 @@
 //
 // Persistent: pair p works on tiles p, p + pairs, ...; two accumulators in tensor
 // memory let the epilogue of one tile overlap the main loop of the next.
+// With few tiles (a few hundred tokens times a narrow matrix) the inner dimension
+// can be cut into `splits` runs: a unit of work is then (tile, run), and run r
+// writes its float32 partial sums to out + r * split_stride for the consumer to
+// add up in index order (as the decode products of gemm_tc.cu do).
 // Barriers: "full" (data of both blocks has landed) lives in block 0; "empty"
 // and "accumulator full" exist in both blocks and are signalled by
 // tcgen05.commit to both; "accumulator empty" lives in block 0 and collects the
@@ -46,6 +50,8 @@ struct Params {
     int pair_offset;               // row offset of the up half inside B
     int out_f32;
     int grid_m, grid_n, total_tiles;
+    int splits;                    // runs of the inner dimension (1: whole)
+    long long split_stride;        // elements between the outputs of two runs
     long long ldo;
     void* out;
     int* status;
@@ -129,10 +135,18 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const uint32_t tmem_base = tmem_base_slot;
     pdl_trigger();
 
+    // unit w = run * tiles + tile: the runs of a tile go to different pairs at the same time
+    const int total_units = p.total_tiles * p.splits;
     auto tile_coords = [&](int w, int& m0, int& n0) {
-        const int x = w % p.grid_m, y = w / p.grid_m;
+        const int tile = w % p.total_tiles;
+        const int x = tile % p.grid_m, y = tile / p.grid_m;
         m0 = x * 2 * BM;
         n0 = y * (GATED ? BNH : BN);
+    };
+    auto k_range = [&](int w, int& k0, int& k1) {
+        const int run = w / p.total_tiles;
+        k0 = (int)((long long)p.k_blocks * run / p.splits);
+        k1 = (int)((long long)p.k_blocks * (run + 1) / p.splits);
     };
 
     if (warp == 0) {
@@ -141,12 +155,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             uint32_t it = 0;
             bool ok = true;
             bool first = true;
-            for (int w = pair_id; w < p.total_tiles && ok; w += n_pairs) {
-                int m0, n0;
+            for (int w = pair_id; w < total_units && ok; w += n_pairs) {
+                int m0, n0, k0, k1;
                 tile_coords(w, m0, n0);
+                k_range(w, k0, k1);
                 const int a_row = m0 + rank * BM;
                 const int b_row = GATED ? (rank == 0 ? n0 : p.pair_offset + n0) : n0 + rank * BNH;
-                for (int i = 0; i < p.k_blocks; ++i, ++it) {
+                for (int i = k0; i < k1; ++i, ++it) {
                     const int s = it % STAGES;
                     const uint32_t round = it / STAGES;
                     if (!mbar_wait(&empty_bar[s], (round & 1) ^ 1, &abort_flag, p.status, 1)) { ok = false; break; }
@@ -167,7 +182,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
             uint32_t it = 0;
             bool ok = true;
             int t = 0;
-            for (int w = pair_id; w < p.total_tiles && ok; w += n_pairs, ++t) {
+            for (int w = pair_id; w < total_units && ok; w += n_pairs, ++t) {
+                int k0, k1;
+                k_range(w, k0, k1);
                 const int buf = t & 1;
                 const uint32_t use = (uint32_t)(t >> 1);
                 if (t > 1) {
@@ -176,7 +193,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     tc_fence_after();
                 }
                 const uint32_t d0 = tmem_base + buf * BN;
-                for (int i = 0; i < p.k_blocks; ++i, ++it) {
+                for (int i = k0; i < k1; ++i, ++it) {
                     const int s = it % STAGES;
                     const uint32_t round = it / STAGES;
                     ok = mbar_wait(&full_bar[s], round & 1, &abort_flag, p.status, 2);
@@ -186,7 +203,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     const uint32_t sb = sa + BM * BK * 2;
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)
-                        tc_mma_pair(d0, smem_desc(sa + k * UMMA_K * 2), smem_desc(sb + k * UMMA_K * 2), idesc, (i > 0 || k > 0) ? 1u : 0u);
+                        tc_mma_pair(d0, smem_desc(sa + k * UMMA_K * 2), smem_desc(sb + k * UMMA_K * 2), idesc, (i > k0 || k > 0) ? 1u : 0u);
                     tc_commit_pair(&empty_bar[s]);     // the stage is free in both blocks
                 }
                 tc_commit_pair(&acc_full[buf]);        // the tile's accumulator is complete in both blocks
@@ -197,9 +214,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         const int q = warp & 3;
         pdl_wait();
         int t = 0;
-        for (int w = pair_id; w < p.total_tiles; w += n_pairs, ++t) {
+        for (int w = pair_id; w < total_units; w += n_pairs, ++t) {
             int m0, n0;
             tile_coords(w, m0, n0);
+            const long long run_off = (long long)(w / p.total_tiles) * p.split_stride;
             const int buf = t & 1;
             const uint32_t use = (uint32_t)(t >> 1);
             const int m = m0 + rank * BM + q * 32 + lane;
@@ -223,7 +241,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
                     }
                     if (m < p.a_rows) {
                         const int n_left = p.b_rows - (n0 + c0);
-                        const long long off = (long long)m * p.ldo + n0 + c0;
+                        const long long off = run_off + (long long)m * p.ldo + n0 + c0;
                         if (OUT_F32) {
                             float* o = (float*)p.out + off;
                             if (n_left >= 16 && (off & 3) == 0) {
@@ -312,13 +330,17 @@ using namespace wick;
 // gated: b holds gate rows [0, b_rows) and up rows [pair_offset, pair_offset + b_rows); the
 // output is silu(a gate^T) * (a up^T).  accumulate (plain float32 output only): out += the product
 // (every element by one thread: no atomics).  b_packed: b in the tiled form described at wick_gemm_tc.
-// status as in wick_gemm_tc.
+// splits > 1 (plain float32 output without accumulation): run r of the inner dimension writes its
+// partial sums to out + r * split_stride.  status as in wick_gemm_tc.
 WICK_API int wick_gemm_tc2(const void* a, int a_rows, const void* b, long long b_total_rows, int b_rows, int k, int gated,
-                           int pair_offset, int out_f32, int accumulate, int b_packed, void* out, long long ldo, int* status, void* stream) {
+                           int pair_offset, int out_f32, int accumulate, int b_packed, void* out, long long ldo, int splits,
+                           long long split_stride, int* status, void* stream) {
     using namespace pair;
     WICK_REQUIRE(a_rows > 0 && b_rows > 0 && k > 0, "gemm_tc2: bad sizes");
     WICK_REQUIRE(gated == 0 || gated == 1, "gemm_tc2: bad options");
     WICK_REQUIRE(!accumulate || (out_f32 && !gated), "gemm_tc2: accumulation goes with a plain float32 output");
+    WICK_REQUIRE(splits >= 1 && (splits == 1 || (out_f32 && !gated && !accumulate)), "gemm_tc2: partial sums are plain float32 outputs");
+    WICK_REQUIRE(splits <= ceil_div(k, BK), "gemm_tc2: %d runs of %d steps", splits, ceil_div(k, BK));
     CUtensorMap map_a, map_b;
     if (int e = make_bf16_map(&map_a, a, a_rows, k, BM, "gemm_tc2")) return e;
     WICK_REQUIRE(!b_packed || (b_total_rows % 128 == 0 && pair_offset % 128 == 0), "gemm_tc2: a packed operand comes in tiles of 128 rows");
@@ -332,7 +354,11 @@ WICK_API int wick_gemm_tc2(const void* a, int a_rows, const void* b, long long b
     const long long total = (long long)p.grid_m * p.grid_n;
     WICK_REQUIRE(total < (1ll << 30), "gemm_tc2: too many tiles");
     p.total_tiles = (int)total;
-    const int pairs = p.total_tiles < 74 ? p.total_tiles : 74;       // 148 SMs
+    p.splits = splits;
+    p.split_stride = split_stride;
+    WICK_REQUIRE(total * splits < (1ll << 30), "gemm_tc2: too many units");
+    const int units = p.total_tiles * splits;
+    const int pairs = units < 74 ? units : 74;                       // 148 SMs
     const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;
     if (gated) return out_f32 ? launch_pair<1, true, false>(map_a, map_b, p, 2 * pairs, smem, (cudaStream_t)stream)
                               : launch_pair<1, false, false>(map_a, map_b, p, 2 * pairs, smem, (cudaStream_t)stream);

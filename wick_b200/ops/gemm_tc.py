@@ -95,9 +95,11 @@ def pack(w: torch.Tensor, gated: bool = False) -> torch.Tensor:
 
 
 def gemm_tc_pair(a: torch.Tensor, b: torch.Tensor, b_rows: int, *, out: torch.Tensor, ldo: int, gated: bool = False,
-                 pair_offset: int = 0, accumulate: bool = False, b_packed: bool = False) -> None:
+                 pair_offset: int = 0, accumulate: bool = False, b_packed: bool = False, splits: int = 1,
+                 split_stride: int = 0) -> None:
     """The kernel for pairs of thread blocks (see ``wick_gemm_tc2`` in gemm_tc2.cu): out[m, n] = a[m] . b[n],
-    or out[m, n] += ... with ``accumulate`` (float32 output)."""
+    or out[m, n] += ... with ``accumulate`` (float32 output), or ``splits`` partial sums over runs of the inner
+    dimension, ``split_stride`` elements apart (float32 output)."""
     for nm, t in (("a", a), ("b", b)):
         if not (t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous()):
             raise KernelError(f"gemm_tc_pair: {nm} must be a contiguous bfloat16 CUDA tensor")
@@ -110,9 +112,9 @@ def gemm_tc_pair(a: torch.Tensor, b: torch.Tensor, b_rows: int, *, out: torch.Te
     if out.dtype not in (torch.float32, torch.bfloat16) or not out.is_contiguous():
         raise KernelError("gemm_tc_pair: out must be contiguous float32 or bfloat16")
     st = status_tensor(a.device)
-    _lib().call("wick_gemm_tc2", "pipliiiiiiiplpp", _p(a), a.shape[0], _p(b), b.shape[0] * 128 if b_packed else b.shape[0],
+    _lib().call("wick_gemm_tc2", "pipliiiiiiiplilpp", _p(a), a.shape[0], _p(b), b.shape[0] * 128 if b_packed else b.shape[0],
                 b_rows, a.shape[1], 1 if gated else 0, pair_offset, 1 if out.dtype == torch.float32 else 0,
-                1 if accumulate else 0, 1 if b_packed else 0, _p(out), ldo, _p(st), _stream())
+                1 if accumulate else 0, 1 if b_packed else 0, _p(out), ldo, splits, split_stride, _p(st), _stream())
 
 
 def _ceil16(n: int) -> int:
@@ -134,6 +136,17 @@ class Plan:
         # Decode: about two blocks per SM (just under 2 x 148) stream best; every
         # split keeps at least eight 64-wide steps of the inner dimension.
         self.decode_splits = max(1, min(2 * N_SMS // tiles, 8, k_blocks // 8))
+        self.k_blocks = k_blocks
+
+    def prompt_splits(self, t: int) -> int:
+        """Runs of the inner dimension for ``t`` >= PAIR_MIN tokens: a few hundred tokens times
+        a narrow matrix make fewer 256 x 256 tiles than there are pairs of SMs (512 tokens
+        x 4096 outputs: 32 tiles for 74 pairs); two to four runs of at least 32 steps each
+        fill the part."""
+        if self.gated:
+            return 1
+        tiles = ((t + 255) // 256) * ((self.n_out + 255) // 256)
+        return max(1, min(4, (N_SMS // 2) // tiles, self.k_blocks // 32))
 
     # ---- [n, in] -> [n, out] ----
     def forward(self, x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
@@ -148,7 +161,7 @@ class Plan:
         t = x.shape[0]
         if self.gated:
             raise KernelError("gemm_tc: a gated pair has no partial sums")
-        splits = self.decode_splits if t <= SMALL else 1
+        splits = self.decode_splits if t <= SMALL else (self.prompt_splits(t) if t >= PAIR_MIN else 1)
         out = torch.empty((splits, t, self.n_out), dtype=torch.float32, device=x.device)
         if t:
             self._run(x, out, splits=splits)
@@ -159,8 +172,8 @@ class Plan:
         kernel for many tokens runs; False (and nothing done) otherwise."""
         t = x.shape[0]
         if self.gated or t < PAIR_MIN or residual.dtype != torch.float32 or not residual.is_contiguous() \
-                or tuple(residual.shape) != (t, self.n_out):
-            return False
+                or tuple(residual.shape) != (t, self.n_out) or self.prompt_splits(t) > 1:
+            return False                                   # (few tiles: partial sums over runs of the inner dimension instead)
         gemm_tc_pair(x, self.w, self.n_out, out=residual, ldo=self.n_out, accumulate=True, b_packed=True)
         return True
 
@@ -173,9 +186,9 @@ class Plan:
             gemm_tc(self.w, self.n_out, x, t, bn=_ceil16(t), out=out, ldo=self.n_out,
                     gated=3 if self.gated else 0, pair_offset=self.pair_offset, transposed=True, splits=splits,
                     split_stride=t * self.n_out, max_smem=100 * 1024, a_static=True, a_packed=True, k=self.k)
-        elif t >= PAIR_MIN and splits == 1:
+        elif t >= PAIR_MIN:
             gemm_tc_pair(x, self.w, self.n_out, out=out, ldo=self.n_out, gated=self.gated, pair_offset=self.pair_offset,
-                         b_packed=True)
+                         b_packed=True, splits=splits, split_stride=t * self.n_out)
         else:
             bn = min(128 if self.gated else 256, _ceil16(self.n_out))
             if bn > 128:
