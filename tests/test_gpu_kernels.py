@@ -486,7 +486,8 @@ def _tc_ref(x, w, gated):
 @pytest.mark.parametrize("t, n, k, gated", [
     (1, 128, 64, False), (5, 333, 72, False), (8, 256, 128, False), (64, 1000, 96, False), (3, 200, 104, True),
     (16, 384, 1024, False), (65, 333, 72, False), (128, 16, 64, False), (300, 520, 200, False), (300, 520, 200, True),
-    (1000, 1024, 512, True), (33, 4096, 4096, False), (8, 1000, 256, True), (40, 333, 2048, True)])
+    (1000, 1024, 512, True), (33, 4096, 4096, False), (8, 1000, 256, True), (40, 333, 2048, True),
+    (100, 520, 2056, False), (255, 4096, 1024, False)])
 def test_gemm_tensor_core_both_ways_round(t, n, k, gated):
     """Few tokens (weights as the 128-row operand, transposed output, split inner
     dimension) and many tokens (tokens as the 128-row operand), plain and gated,
@@ -507,8 +508,8 @@ def test_gemm_tensor_core_both_ways_round(t, n, k, gated):
         parts = plan.forward_delta(dev(x))
         assert parts.dtype == torch.float32 and parts.shape[1:] == (t, n)
         assert (parts.sum(0).cpu() - ref).abs().max() < 2e-4 * max(1.0, ref.abs().max())
-        if t <= G.SMALL and k >= 1024:
-            assert parts.shape[0] > 1, "a matrix with few row slabs splits its inner dimension"
+        if t < G.PAIR_MIN and k >= 1024:
+            assert parts.shape[0] > 1, "a product with few tiles splits its inner dimension"
     G.check_status()
     # the CUDA-core kernel is the plain twin of this one
     twin = ops_gemm_simt(dev(x), dev(w), gated)

@@ -215,7 +215,8 @@ class Engine:
         batch = StepBatch(layout, dev, q_lens=q_lens, starts=starts)
         batch.workspace = self.workspace
         batch.kv_bound = batch.max_kv_len
-        logits = self.model.forward(batch, cache)
+        with ops.stream_scope():
+            logits = self.model.forward(batch, cache)
         self._steps_since_check += 1
         if self._steps_since_check >= 64:
             self.check_kernels()
@@ -273,7 +274,8 @@ class Engine:
             batch = StepBatch(g.layout, g.buffer, q_lens=q_lens, starts=[0] * g.n_pad)
             batch.workspace = self.workspace
             batch.kv_bound = kv_bound
-            return self.model.forward(batch, self.cache)
+            with ops.stream_scope():                # (entered on the stream that runs or captures the step)
+                return self.model.forward(batch, self.cache)
 
         # Warm-up outside capture (compiles/loads kernels, grows scratch buffers).
         s = torch.cuda.Stream()

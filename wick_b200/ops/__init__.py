@@ -8,10 +8,11 @@ any kind: without a CUDA device or without ``nvcc`` these functions raise.
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
-import os
 import math
-from typing import Dict, Optional, Tuple
+import os
+from typing import Dict, List, Optional, Tuple
 
 import torch
 
@@ -131,8 +132,25 @@ def _p(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
 
 
+_scope_stream: List[Optional[int]] = [None]
+
+
+@contextlib.contextmanager
+def stream_scope():
+    """Inside the scope every kernel of this module goes to the stream that is
+    current at entry.  (Asked once: torch's lookup of the current stream costs as
+    much host time as a launch, and a short prompt's step is bound by the host.)"""
+    before = _scope_stream[0]
+    _scope_stream[0] = torch.cuda.current_stream().cuda_stream
+    try:
+        yield
+    finally:
+        _scope_stream[0] = before
+
+
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    s = _scope_stream[0]
+    return torch.cuda.current_stream().cuda_stream if s is None else s
 
 
 def _need(cond: bool, msg: str) -> None:

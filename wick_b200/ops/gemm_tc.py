@@ -3,16 +3,19 @@
 A plan belongs to one bfloat16 weight matrix [out, in] and decides, per call,
 which way round the kernel runs:
 
-* few tokens (at most 64): the weights are the 128-row operand, the tokens the
+* fewer than 256 tokens: the weights are the 128-row operand, the tokens the
   narrow one (tile width = tokens rounded up to 16), the result is written
   transposed.  Matrices with few 128-row slabs split their inner dimension over
   several blocks, so that enough of them stream weights at once; the float32
-  partial sums are added by the consumer in index order.  The number of splits
-  depends on the matrix alone, never on the batch.
-* more tokens: the tokens are the 128-row operand, weight tiles are 256 rows
-  (128 + 128 for a gated pair) wide.
+  partial sums are added by the consumer in index order.  Up to 64 tokens (a
+  decode step) the number of splits depends on the matrix alone, never on the
+  batch, and two blocks of 100 KB share an SM; short prompts of 65 to 255 tokens
+  take fewer splits (and one 200 KB block per SM beyond 128 tokens).
 * 256 tokens and more: the kernel of ``csrc/gemm_tc2.cu``, in which two thread
-  blocks on neighbouring SMs share one 256 x 256 tile.
+  blocks on neighbouring SMs share one 256 x 256 tile (few tiles: the inner
+  dimension in 2 to 4 runs).
+* the tokens as the 128-row operand of single blocks (weight tiles 256 rows wide,
+  128 + 128 for a gated pair) is the form the tests hold the pair kernel against.
 
 Inner sizes that are no multiple of 8 (rows that are no multiple of 16 bytes
 cannot be fetched by TMA) have no plan; the caller then uses the CUDA-core kernel.
@@ -25,7 +28,9 @@ import torch
 
 from . import KernelError, _Lib, _libs, _p, _stream, check_status, status_tensor  # noqa: F401
 
-SMALL = 64                  # up to this many tokens the weights are the 128-row operand
+SMALL = 64                  # up to this many tokens: weights as the 128-row operand, two 100 KB blocks per SM
+SWAP_MAX = 255              # up to this many tokens: weights as the 128-row operand (measured: 5-14 % faster than
+                            # tokens on the 128-row side for 100-200 tokens, whose one or two slabs leave SMs idle)
 PAIR_MIN = 256              # from this many tokens on, pairs of thread blocks share 256 x 256 tiles
 N_SMS = 148
 
@@ -148,6 +153,15 @@ class Plan:
         tiles = ((t + 255) // 256) * ((self.n_out + 255) // 256)
         return max(1, min(4, (N_SMS // 2) // tiles, self.k_blocks // 32))
 
+    def mid_splits(self, t: int) -> int:
+        """Runs of the inner dimension for SMALL < ``t`` < PAIR_MIN tokens (a short prompt):
+        one or two 128-row slabs of tokens times 256-wide slabs of the matrix are a handful of
+        tiles; up to eight runs of at least eight steps each give every SM a block."""
+        if self.gated:
+            return 1
+        tiles = ((t + 127) // 128) * ((self.n_out + 255) // 256)
+        return max(1, min(8, N_SMS // tiles, self.k_blocks // 8))
+
     # ---- [n, in] -> [n, out] ----
     def forward(self, x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
         t = x.shape[0]
@@ -161,7 +175,12 @@ class Plan:
         t = x.shape[0]
         if self.gated:
             raise KernelError("gemm_tc: a gated pair has no partial sums")
-        splits = self.decode_splits if t <= SMALL else (self.prompt_splits(t) if t >= PAIR_MIN else 1)
+        if t <= SMALL:
+            splits = self.decode_splits
+        elif t <= SWAP_MAX:
+            splits = max(1, min(N_SMS // ((self.n_out + 127) // 128), 8, self.k_blocks // 8))
+        else:
+            splits = self.prompt_splits(t) if t >= PAIR_MIN else self.mid_splits(t)
         out = torch.empty((splits, t, self.n_out), dtype=torch.float32, device=x.device)
         if t:
             self._run(x, out, splits=splits)
@@ -179,13 +198,15 @@ class Plan:
 
     def _run(self, x: torch.Tensor, out: torch.Tensor, splits: int) -> None:
         t = x.shape[0]
-        if t <= SMALL:
+        if t <= max(SMALL, SWAP_MAX):
             # Two blocks of 100 KB per SM: one block's start and end overlap the
             # other's streaming.  A gated pair shares one 128-row tile (64 gate rows,
-            # 64 up rows), which doubles the number of blocks.
+            # 64 up rows), which doubles the number of blocks.  (More than 128 tokens make
+            # stages of 48 KB: one block of 200 KB per SM then.)
             gemm_tc(self.w, self.n_out, x, t, bn=_ceil16(t), out=out, ldo=self.n_out,
                     gated=3 if self.gated else 0, pair_offset=self.pair_offset, transposed=True, splits=splits,
-                    split_stride=t * self.n_out, max_smem=100 * 1024, a_static=True, a_packed=True, k=self.k)
+                    split_stride=t * self.n_out, max_smem=(100 if t <= 128 else 200) * 1024, a_static=True,
+                    a_packed=True, k=self.k)
         elif t >= PAIR_MIN:
             gemm_tc_pair(x, self.w, self.n_out, out=out, ldo=self.n_out, gated=self.gated, pair_offset=self.pair_offset,
                          b_packed=True, splits=splits, split_stride=t * self.n_out)
