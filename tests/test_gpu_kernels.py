@@ -487,7 +487,7 @@ def _tc_ref(x, w, gated):
     (1, 128, 64, False), (5, 333, 72, False), (8, 256, 128, False), (64, 1000, 96, False), (3, 200, 104, True),
     (16, 384, 1024, False), (65, 333, 72, False), (128, 16, 64, False), (300, 520, 200, False), (300, 520, 200, True),
     (1000, 1024, 512, True), (33, 4096, 4096, False), (8, 1000, 256, True), (40, 333, 2048, True),
-    (100, 520, 2056, False), (255, 4096, 1024, False)])
+    (100, 520, 2056, False), (255, 4096, 1024, False), (100, 333, 328, True), (255, 520, 200, True), (130, 1000, 4096, True)])
 def test_gemm_tensor_core_both_ways_round(t, n, k, gated):
     """Few tokens (weights as the 128-row operand, transposed output, split inner
     dimension) and many tokens (tokens as the 128-row operand), plain and gated,
