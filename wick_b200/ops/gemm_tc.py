@@ -153,10 +153,16 @@ class Plan:
         tiles = ((t + 255) // 256) * ((self.n_out + 255) // 256)
         return max(1, min(4, (N_SMS // 2) // tiles, self.k_blocks // 32))
 
+    def short_prompt_splits(self) -> int:
+        """Runs of the inner dimension for SMALL < tokens <= SWAP_MAX (weights as the 128-row
+        operand, at most one block per SM)."""
+        return max(1, min(N_SMS // ((self.n_out + 127) // 128), 8, self.k_blocks // 8))
+
     def mid_splits(self, t: int) -> int:
-        """Runs of the inner dimension for SMALL < ``t`` < PAIR_MIN tokens (a short prompt):
-        one or two 128-row slabs of tokens times 256-wide slabs of the matrix are a handful of
-        tiles; up to eight runs of at least eight steps each give every SM a block."""
+        """Runs of the inner dimension when SWAP_MAX < ``t`` < PAIR_MIN tokens take the form with
+        the tokens as the 128-row operand of single blocks: one or two slabs of tokens times
+        256-wide slabs of the matrix are a handful of tiles; up to eight runs of at least eight
+        steps each give every SM a block."""
         if self.gated:
             return 1
         tiles = ((t + 127) // 128) * ((self.n_out + 255) // 256)
@@ -178,7 +184,7 @@ class Plan:
         if t <= SMALL:
             splits = self.decode_splits
         elif t <= SWAP_MAX:
-            splits = max(1, min(N_SMS // ((self.n_out + 127) // 128), 8, self.k_blocks // 8))
+            splits = self.short_prompt_splits()
         else:
             splits = self.prompt_splits(t) if t >= PAIR_MIN else self.mid_splits(t)
         out = torch.empty((splits, t, self.n_out), dtype=torch.float32, device=x.device)
