@@ -24,3 +24,23 @@ def test_pack_pads_the_halves_of_a_gated_pair_separately():
     assert p.shape == (4, 1, 128, 64)
     assert torch.equal(p[0, 0], w[:128]) and torch.equal(p[1, 0, :2], w[128:130]) and (p[1, 0, 2:] == 0).all()
     assert torch.equal(p[2, 0], w[130:258]) and torch.equal(p[3, 0, :2], w[258:260]) and (p[3, 0, 2:] == 0).all()
+
+
+def test_how_a_plan_cuts_the_inner_dimension_at_the_sizes_of_qwen3_8b():
+    """The rules that decide how many blocks stream a matrix, at the shapes the bench
+    runs (hidden 4096, q 4096 + kv 2 x 1024, intermediate 12288).  Pure host logic."""
+    from wick_b200.ops.gemm_tc import Plan
+    qkv = Plan(torch.zeros(6144, 4096, dtype=torch.bfloat16), False)
+    o = Plan(torch.zeros(4096, 4096, dtype=torch.bfloat16), False)
+    down = Plan(torch.zeros(4096, 12288, dtype=torch.bfloat16), False)
+    gate_up = Plan(torch.zeros(2 * 1024, 4096, dtype=torch.bfloat16), True)
+    # decode steps (up to 64 tokens): about two blocks per SM, the same for every batch
+    assert (qkv.decode_splits, o.decode_splits, down.decode_splits) == (6, 8, 8)
+    # short prompts (65 to 255 tokens): at most one block per SM
+    assert (qkv.short_prompt_splits(), o.short_prompt_splits(), down.short_prompt_splits()) == (3, 4, 4)
+    # prompts on pairs of thread blocks: runs only where 256 x 256 tiles are few
+    assert [o.prompt_splits(t) for t in (256, 512, 1024, 2048)] == [2, 2, 1, 1]
+    assert [down.prompt_splits(t) for t in (256, 512, 1024, 2048)] == [4, 2, 1, 1]
+    assert [qkv.prompt_splits(t) for t in (256, 512, 2048)] == [2, 1, 1]
+    assert gate_up.prompt_splits(256) == 1 and gate_up.mid_splits(100) == 1, "a gated pair has no partial sums"
+    assert gate_up.pair_offset == 1024 and gate_up.n_out == 1024
