@@ -234,15 +234,21 @@ def _many_lengths(n, seed):
 @pytest.mark.parametrize("heads, kv_heads, hd, lens", [(8, 2, 128, (1, 130, 700, 64)), (4, 4, 64, (129, 5)),
                                                         (16, 2, 128, (300,)), (6, 2, 64, (2000, 65, 128, 127, 1, 1025)),
                                                         (8, 2, 128, _many_lengths(74, 1)), (6, 3, 64, _many_lengths(49, 2)),
-                                                        (8, 8, 128, _many_lengths(18, 3)), (4, 1, 128, _many_lengths(148, 4))])
+                                                        (8, 8, 128, _many_lengths(18, 3)), (4, 1, 128, _many_lengths(148, 4)),
+                                                        (8, 2, 128, _many_lengths(100, 1)), (6, 3, 64, _many_lengths(75, 2)),
+                                                        (8, 8, 128, _many_lengths(19, 3)), (4, 1, 128, _many_lengths(300, 4)),
+                                                        (32, 8, 128, (1537,) * 24 + (1, 700, 1300, 128))])
 def test_decode_attention_in_one_kernel(ops, heads, kv_heads, hd, lens):
     """The fused decode kernel (norm, rotation, cache append, attention, merge) against
     the three kernels it replaces, on the same float32 partial sums: same output, and
     the same key and value rows in the cache.  Lengths around the 128-position chunk
     and the 64-position page; scrambled pages; NaN wherever the cache holds no token.
-    The last four cases have 144 to 148 (sequence, kv head) pairs: a block each, no clusters."""
+    Up to 148 (sequence, kv head) pairs take the kernel that spreads a pair over a cluster
+    (144 to 148 pairs: a block each); more (the last five cases: 200, 225, 152, 300 and 224
+    pairs, the last with 13 chunks a job) the persistent one, whose blocks have 1 to 3 jobs
+    and pairs of warps with unequal numbers of them."""
     assert ops.attention_decode_fused_supported(len(lens), heads, kv_heads, hd, torch.bfloat16)
-    assert not ops.attention_decode_fused_supported(200, heads, kv_heads, hd, torch.bfloat16)
+    assert ops._fused_kind(len(lens), heads, kv_heads, hd, torch.bfloat16) == ("fused" if len(lens) * kv_heads <= 148 else "stream")
     assert not ops.attention_decode_fused_supported(4, 18, 2, hd, torch.bfloat16), "9 query heads per kv head"
     torch.manual_seed(hd + heads + len(lens))
     B = len(lens)

@@ -44,6 +44,7 @@ static_assert(Q_BYTES <= 2048 || !SUPPORTED, "the query rows of an item fit the 
 constexpr int STAGES = 3;
 constexpr int KS = HD / 16;
 constexpr int GROUPS = 2;                              // independent pairs of compute warps (items alternate between them)
+static_assert(STAGES == 3 && GROUPS == 2, "the barriers count on a pair meeting a stage every STAGES * GROUPS items");
 constexpr int CWARPS = GROUPS * PAGES;
 constexpr int THREADS = (CWARPS + 1) * 32;             // compute warps (one page each), then the producer warp
 constexpr int MAX_SEQS = 512;
@@ -82,7 +83,12 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* _
     __shared__ float m_all[GROUPS][PAGES][NH], l_all[GROUPS][PAGES][NH];
     __shared__ int cum[MAX_SEQS + 1];                    // items before each sequence
     __shared__ int kvl[MAX_SEQS];                        // cached positions of each sequence
-    __shared__ uint64_t full_k[STAGES], full_v[STAGES], empty[STAGES];
+    // Barriers per (stage, pair of warps).  Item n goes to stage n % 3 and to pair n % 2, so a pair
+    // comes back to a stage every sixth item: with one barrier per stage for both pairs, a pair's
+    // wait would lie two phases after its last one, which a parity cannot tell from none, and the
+    // wait would hold only as long as copies complete in the order they were issued.  With a
+    // barrier of its own, every waiter sees every phase: visit n / 6 has parity (n / 6) & 1.
+    __shared__ uint64_t full_k[STAGES][GROUPS], full_v[STAGES][GROUPS], empty[STAGES][GROUPS];
     __shared__ int abort_flag, stop_s[GROUPS];
 
     pdl_trigger();
@@ -113,11 +119,12 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* _
     }
     if (tid == 0) {
         abort_flag = 0;
-        for (int s = 0; s < STAGES; ++s) {
-            mbar_init(&full_k[s], 1);
-            mbar_init(&full_v[s], 1);
-            mbar_init(&empty[s], PAGES);                 // one arrival per compute warp
-        }
+        for (int s = 0; s < STAGES; ++s)
+            for (int g = 0; g < GROUPS; ++g) {
+                mbar_init(&full_k[s][g], 1);
+                mbar_init(&full_v[s][g], 1);
+                mbar_init(&empty[s][g], PAGES);          // one arrival per compute warp of the pair
+            }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     // query rows beyond a group's heads stay zero for the whole kernel
@@ -151,27 +158,27 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* _
         if (lane == 0) {
             int n = 0;
             for (int item = blockIdx.x; item < total; item += gridDim.x, ++n) {
-                const int s = n % STAGES;
-                const uint32_t round = n / STAGES;
-                if (!mbar_wait(&empty[s], (round & 1) ^ 1, &abort_flag, status, 6)) break;
+                const int s = n % STAGES, g = n % GROUPS;
+                // the stage held item n - 3, of the other pair: free when that pair has used it
+                if (n >= STAGES && !mbar_wait(&empty[s][(n - STAGES) % GROUPS], ((n - STAGES) / (STAGES * GROUPS)) & 1, &abort_flag, status, 6)) break;
                 Item it;
                 decode(item, it);
                 const int key_begin = it.split * SPLIT;
                 const int n_pages = min(PAGES, (it.kv_len - key_begin + kPage - 1) / kPage);
                 uint8_t* st = stages + (size_t)s * STAGE_BYTES;
                 const uint32_t q_bytes = (uint32_t)it.nh * HD * 2;
-                mbar_expect_tx(&full_k[s], (uint32_t)(n_pages * TILE_BYTES) + q_bytes);
-                bulk_load(st + 2 * PAGES * TILE_BYTES, q + ((int64_t)it.b * n_heads + it.kvh * group + it.h0) * HD, q_bytes, &full_k[s]);
+                mbar_expect_tx(&full_k[s][g], (uint32_t)(n_pages * TILE_BYTES) + q_bytes);
+                bulk_load(st + 2 * PAGES * TILE_BYTES, q + ((int64_t)it.b * n_heads + it.kvh * group + it.h0) * HD, q_bytes, &full_k[s][g]);
                 for (int w = 0; w < n_pages; ++w) {
                     const int page = page_table[(int64_t)it.b * table_width + key_begin / kPage + w];
                     const int row = ((page * 2 + 0) * n_kv + it.kvh) * kPage;
-                    for (int pn = 0; pn < PANELS; ++pn) tma_load_2d(&kv_map, &full_k[s], st + w * TILE_BYTES + pn * PANEL_BYTES, pn * 64, row);
+                    for (int pn = 0; pn < PANELS; ++pn) tma_load_2d(&kv_map, &full_k[s][g], st + w * TILE_BYTES + pn * PANEL_BYTES, pn * 64, row);
                 }
-                mbar_expect_tx(&full_v[s], (uint32_t)(n_pages * TILE_BYTES));
+                mbar_expect_tx(&full_v[s][g], (uint32_t)(n_pages * TILE_BYTES));
                 for (int w = 0; w < n_pages; ++w) {
                     const int page = page_table[(int64_t)it.b * table_width + key_begin / kPage + w];
                     const int row = ((page * 2 + 1) * n_kv + it.kvh) * kPage;
-                    for (int pn = 0; pn < PANELS; ++pn) tma_load_2d(&kv_map, &full_v[s], st + (PAGES + w) * TILE_BYTES + pn * PANEL_BYTES, pn * 64, row);
+                    for (int pn = 0; pn < PANELS; ++pn) tma_load_2d(&kv_map, &full_v[s][g], st + (PAGES + w) * TILE_BYTES + pn * PANEL_BYTES, pn * 64, row);
                 }
             }
         }
@@ -191,7 +198,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* _
             const int item = blockIdx.x + n * gridDim.x;
             if (item >= total) break;
             const int s = n % STAGES;
-            const uint32_t round = n / STAGES;
+            const uint32_t visit = (uint32_t)n / (STAGES * GROUPS);     // this pair's visits to this stage so far
             Item it;
             decode(item, it);
             const int key_begin = it.split * SPLIT;
@@ -202,7 +209,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* _
             const uint32_t k_base = smem_u32(st + wp * TILE_BYTES), v_base = smem_u32(st + (PAGES + wp) * TILE_BYTES);
             const bf16* q_s = reinterpret_cast<const bf16*>(st + 2 * PAGES * TILE_BYTES);
 
-            bool ok = mbar_wait(&full_k[s], round & 1, &abort_flag, status, 6);
+            bool ok = mbar_wait(&full_k[s][grp], visit & 1, &abort_flag, status, 6);
             // ---- scores S^T[key, head] of this warp's page ----
             float sc[4][4];
             float mx0 = -INFINITY, mx1 = -INFINITY;
@@ -261,7 +268,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* _
                 l1 += __shfl_xor_sync(0xffffffffu, l1, o);
             }
             if (lane < 4) { l_w[wp][c0] = l0; l_w[wp][c0 + 1] = l1; }
-            ok = mbar_wait(&full_v[s], round & 1, &abort_flag, status, 6) && ok;
+            ok = mbar_wait(&full_v[s][grp], visit & 1, &abort_flag, status, 6) && ok;
             // Rows of the last page that hold no token yet may be anything: make them
             // zero, so that a zero weight times such a row stays zero.
             if (live && ok && keys_here < kPage) {
@@ -291,7 +298,7 @@ attn_decode_mma_kernel(const __grid_constant__ CUtensorMap kv_map, const bf16* _
             }
             // this warp has read all it needs of the stage
             __syncwarp();
-            if (lane == 0) mbar_arrive_cta(&empty[s]);
+            if (lane == 0) mbar_arrive_cta(&empty[s][grp]);
             // ---- warp 1 hands its part to warp 0, which writes the item's partial result ----
             if (wp == 1) {
 #pragma unroll

@@ -87,7 +87,8 @@ def _simt() -> _Lib:
     return lib
 
 
-ATTN_SOURCES = ["attn.cu", "attn_decode.cu", "attn_decode_mma.cu", "attn_decode_fused.cu", "attn_prompt_mma.cu", "attn_prompt_tc.cu"]
+ATTN_SOURCES = ["attn.cu", "attn_decode.cu", "attn_decode_mma.cu", "attn_decode_fused.cu", "attn_decode_stream.cu",
+                "attn_prompt_mma.cu", "attn_prompt_tc.cu"]
 
 
 def _attn(head_dim: int) -> _Lib:
@@ -108,7 +109,7 @@ _status: Optional[torch.Tensor] = None
 _STATUS_TEXT = {1: "gemm_tc: a free shared-memory stage", 2: "gemm_tc: a TMA copy", 3: "gemm_tc: the accumulator",
                 4: "attention decode: its bulk copies", 5: "gemm_tc: a free accumulator",
                 6: "attention decode (tensor cores): its TMA copies", 7: "attention (tcgen05): a copy or an accumulator",
-                8: "attention decode (fused): its TMA copies"}
+                8: "attention decode (fused): its TMA copies", 10: "attention decode: a page outside the cache"}
 
 
 def status_tensor(device) -> torch.Tensor:
@@ -422,20 +423,29 @@ _fused_ok: Dict[tuple, bool] = {}
 
 
 def attention_decode_fused_supported(n_seqs: int, n_heads: int, n_kv: int, head_dim: int, dtype: torch.dtype) -> bool:
-    """Whether the one-kernel decode attention (q/k norm, rotation, cache append,
+    """Whether a one-kernel decode attention (q/k norm, rotation, cache append,
     attention and merge in one launch) takes this problem: bfloat16, head size 64
-    or 128, at most 8 query heads per kv head, and few enough (sequence, kv head)
-    pairs for all of its blocks to run at once."""
+    or 128, at most 8 query heads per kv head.  (Two kernels: one that spreads a
+    (sequence, kv head) pair over a cluster of blocks, for as many pairs as run at
+    once, and one with persistent blocks for more.)"""
+    return _fused_kind(n_seqs, n_heads, n_kv, head_dim, dtype) is not None
+
+
+def _fused_kind(n_seqs: int, n_heads: int, n_kv: int, head_dim: int, dtype: torch.dtype) -> Optional[str]:
     if dtype != torch.bfloat16 or head_dim not in (64, 128) or os.environ.get("WICK_B200_NO_FUSED_DECODE"):
-        return False
+        return None
     key = (n_seqs, n_heads, n_kv, head_dim)
-    v = _fused_ok.get(key)
-    if v is None:
-        f = _attn(head_dim)._lib.wick_attn_decode_fused_supported
-        f.restype = ctypes.c_int
-        f.argtypes = [ctypes.c_int] * 3
-        v = _fused_ok[key] = bool(f(n_seqs, n_heads, n_kv))
-    return v
+    if key not in _fused_ok:
+        kind = None
+        for name in ("fused", "stream"):
+            f = getattr(_attn(head_dim)._lib, f"wick_attn_decode_{name}_supported")
+            f.restype = ctypes.c_int
+            f.argtypes = [ctypes.c_int] * 3
+            if f(n_seqs, n_heads, n_kv) and not (name == "stream" and os.environ.get("WICK_B200_NO_STREAM_DECODE")):
+                kind = name
+                break
+        _fused_ok[key] = kind
+    return _fused_ok[key]
 
 
 def attention_decode_fused(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, *,
@@ -466,7 +476,9 @@ def attention_decode_fused(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim:
         out = torch.empty((n, n_heads, head_dim), dtype=torch.bfloat16, device=qkv.device)
     _cuda("out", out, torch.bfloat16, (n, n_heads, head_dim))
     mk = batch.max_kv_len if max_kv_len is None else max_kv_len
-    _attn(head_dim).call("wick_attn_decode_fused_bf16", "piippfppplppipiiifipp", _p(qkv), qkv.shape[0], n, _p(q_weight),
+    kind = _fused_kind(n, n_heads, n_kv, head_dim, torch.bfloat16)
+    _need(kind is not None, f"no one-kernel decode attention for {n} sequences, {n_heads} heads over {n_kv} kv heads of {head_dim}")
+    _attn(head_dim).call(f"wick_attn_decode_{kind}_bf16", "piippfppplppipiiifipp", _p(qkv), qkv.shape[0], n, _p(q_weight),
                          _p(k_weight), float(eps), _p(cos), _p(sin), _p(kv), kv.shape[0], _p(out), _p(batch.kv_len), mk,
                          _p(batch.page_table), batch.table_width, n_heads, n_kv, float(scale), 1 if write_kv else 0,
                          _p(status_tensor(qkv.device)), _stream())
