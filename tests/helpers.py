@@ -33,13 +33,13 @@ CONFIG_C = dict(architectures=["Qwen3ForCausalLM"], hidden_size=72, num_attentio
 # D: head_dim 64 with a group of 4, the sizes at which the bfloat16 path takes its
 # tensor-core attention kernels for decode as well as for prompts.
 CONFIG_D = dict(architectures=["Qwen3ForCausalLM"], hidden_size=128, num_attention_heads=8, num_key_value_heads=2,
-                head_dim=64, intermediate_size=256, num_hidden_layers=2, vocab_size=640, max_position_embeddings=1024,
+                head_dim=64, intermediate_size=256, num_hidden_layers=2, vocab_size=640, max_position_embeddings=2048,
                 rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=True)
 # E: head_dim 128 with ONE kv head and narrow matrices: every kernel of a decode
 # step is short, so a captured step overlaps each kernel with the end of the one
 # before it as far as programmatic dependent launch allows.
 CONFIG_E = dict(architectures=["Qwen3ForCausalLM"], hidden_size=256, num_attention_heads=4, num_key_value_heads=1,
-                head_dim=128, intermediate_size=384, num_hidden_layers=2, vocab_size=1003, max_position_embeddings=1024,
+                head_dim=128, intermediate_size=384, num_hidden_layers=2, vocab_size=1003, max_position_embeddings=2048,
                 rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=True)
 # R: one layer with the real widths of Qwen3-8B (hidden 4096, 32 heads over 8 kv
 # heads of 128, intermediate 12288) and a vocabulary that is no multiple of the

@@ -291,3 +291,104 @@ def test_real_layer_widths_of_qwen3_8b(dtype, lens):
             assert_logits_close(got[i], refs[i][h + k], dtype, f"R seq {i} decode {k}")
     for s in slots:
         eng.close_seq(s)
+
+
+def _run_batch_against_plain(name, dtype, eng, lens, n_decode, seed0, every=1):
+    """Prompts of ``lens`` tokens in one step, then ``n_decode[i]`` tokens one by one for
+    sequence i (shorter ones leave earlier); every logit row against the plain implementation."""
+    seqs = [random_tokens(vocab_of(name), n + d, seed0 + i) for i, (n, d) in enumerate(zip(lens, n_decode))]
+    refs = [plain_logits(name, s) for s in seqs]
+    slots = [eng.open_seq() for _ in seqs]
+    got = eng.step(slots, [s[:n] for s, n in zip(seqs, lens)], [[n - 1] for n in lens]).clone()
+    for i, n in enumerate(lens):
+        assert_logits_close(got[i], refs[i][n - 1], dtype, f"{name} prompt {i} of {n} tokens")
+    live = [i for i in range(len(seqs)) if n_decode[i] > 0]
+    for i in range(len(seqs)):
+        if n_decode[i] == 0:
+            eng.close_seq(slots[i])
+    step = 0
+    while live:
+        got = eng.step([slots[i] for i in live], [[seqs[i][lens[i] + step]] for i in live]).clone()
+        if step % every == 0 or step + 1 >= max(n_decode):
+            for r, i in enumerate(live):
+                assert_logits_close(got[r], refs[i][lens[i] + step], dtype, f"{name} seq {i} ({lens[i]} tokens) decode step {step}")
+        step += 1
+        for i in list(live):
+            if step >= n_decode[i]:
+                eng.close_seq(slots[i])
+                live.remove(i)
+        poison_free_pages(eng)
+    eng.cache.check()
+    assert eng.cache.pages.n_held == 0
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_decode_batch_beyond_148_pairs_at_real_widths(dtype, graphs):
+    """22 sequences of 1 to 700 tokens at the real widths (config R: 8 kv heads, so 176
+    (sequence, kv head) pairs): the prompts in one step, then up to 9 decoded tokens each,
+    the shorter requests leaving earlier, so that the batch runs at 22, 19, 17 ... sequences
+    (batch buckets 32 and 16) and the decode attention for many pairs runs inside the engine."""
+    name = "R"
+    lens = (1, 700, 3, 64, 65, 127, 128, 129, 130, 2, 255, 256, 257, 31, 300, 20, 5, 385, 77, 200, 192, 193)
+    n_decode = tuple(9 - (i % 4) * 2 if i % 5 else 9 for i in range(len(lens)))
+    eng = make_engine(name, dtype, max_tokens=sum((n + 9 + 63) // 64 * 64 for n in lens), use_graphs=graphs)
+    poison_all(eng)
+    _run_batch_against_plain(name, dtype, eng, lens, n_decode, 3000)
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_decode_batch_of_80_sequences(dtype, graphs):
+    """Config D (2 kv heads of 64) with 80 sequences: 160 pairs, the batch bucket of 128,
+    then 64 as requests leave."""
+    name = "D"
+    g = torch.Generator().manual_seed(5)
+    lens = tuple(int(x) for x in torch.randint(1, 330, (80,), generator=g))
+    n_decode = tuple(3 + (i * 7) % 10 for i in range(80))
+    eng = make_engine(name, dtype, max_tokens=sum((n + 12 + 63) // 64 * 64 for n in lens), use_graphs=graphs)
+    poison_all(eng)
+    _run_batch_against_plain(name, dtype, eng, lens, n_decode, 4000)
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_decoding_across_512_and_1024_cached_tokens(name, dtype, graphs):
+    """Sequences decode across 512 and across 1,024 cached positions: a captured step is made
+    for page tables of 8, 16 and 32 pages, and a live sequence changes from one captured step
+    to the next in mid-flight."""
+    eng = make_engine(name, dtype, max_tokens=4096, use_graphs=graphs)
+    poison_all(eng)
+    _run_batch_against_plain(name, dtype, eng, (500, 40), (30, 12), 5000 + len(name))
+    _run_batch_against_plain(name, dtype, eng, (1015, 300, 7), (30, 30, 5), 5100 + len(name))
+    if graphs:
+        widths = sorted(set(w for (_, w) in eng._graphs))
+        assert widths == [8, 16, 32], widths
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_batch_composition_changes_no_bit_with_tensor_core_attention(name, dtype, graphs):
+    """Head sizes 64 and 128 (in bfloat16 the one-launch decode attention): a request of 1,100
+    cached tokens (nine runs of 128 positions) decoded alone, among 3 and among 24 gives the
+    same bits, eagerly and from captured steps: how a sequence's positions are cut into runs,
+    and the order in which the runs' results are merged, depend on its own length only."""
+    eng = make_engine(name, dtype, max_tokens=8192, use_graphs=graphs)
+    lens = [1100, 6, 77, 500, 9] + [20 + 11 * i for i in range(19)]
+    seqs = [random_tokens(vocab_of(name), n + 4, 40 + n) for n in lens]
+    outs = {}
+    for count in (1, 3, 24):
+        group = list(range(count))
+        slots = [eng.open_seq() for _ in group]
+        eng.step(slots, [seqs[i][:-4] for i in group], [[] for _ in group])
+        rows = []
+        for k in range(4, 0, -1):
+            rows.append(eng.step(slots, [[seqs[i][-k]] for i in group])[0].clone())
+        for s in slots:
+            eng.close_seq(s)
+        outs[count] = torch.stack(rows)
+    assert_logits_close(outs[24], plain_logits(name, seqs[0])[-4:], dtype, "batched decode")
+    assert torch.equal(outs[1], outs[3]), "alone and among 3"
+    assert torch.equal(outs[1], outs[24]), "alone and among 24"

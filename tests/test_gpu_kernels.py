@@ -282,6 +282,15 @@ def test_decode_attention_in_one_kernel(ops, heads, kv_heads, hd, lens):
     ops.check_status()
     assert torch.isfinite(got).all()
     assert (got - want).abs().max() < tol(torch.bfloat16, 1)
+    # ... and against the plain attention over the cache as it now stands (bfloat16 keys and
+    # values read back page by page, the bfloat16 query rows of the three-kernel path)
+    for b, t in enumerate(lens):
+        kk = torch.cat([kv_b[pg, 0].float() for pg in pages[b]], dim=1)[:, :t].transpose(0, 1).cpu()
+        vv = torch.cat([kv_b[pg, 1].float() for pg in pages[b]], dim=1)[:, :t].transpose(0, 1).cpu()
+        qq = q[b].float().cpu()                                  # the last row of a causal attention sees every key
+        ref = torch.stack([P.softmax_rows(((qq[h] @ kk[:, h // (heads // kv_heads)].T) * scale)[None])[0]
+                           @ vv[:, h // (heads // kv_heads)] for h in range(heads)])
+        assert (got[b].cpu() - ref).abs().max() < tol(torch.bfloat16, 1), f"sequence {b} of {t} positions"
     # The new token's rows, and nothing else, were written.  (The kernels add the squares of a head
     # in different orders: a key may differ in its last bfloat16 bit.)
     for b, t in enumerate(lens):
