@@ -140,3 +140,98 @@ def test_on_step_sees_who_is_still_running():
     generate(e, [[1], [30]], GenOptions(max_tokens=3, sampler=SamplerConfig.greedy(), stop_token_ids=[3]),
              sampler_factory=CpuGreedy, on_step=lambda n, live: seen.append((n, list(live))))
     assert seen == [(1, [0, 1]), (2, [1]), (3, [])]
+
+
+class LaggingRun:
+    """A batch stepped one step ahead of what the loop has read, the way the device-side
+    run is: ``launch`` feeds every sequence the token sampled for it last, a sequence that
+    sampled a stop token or reached its limit is frozen (it keeps its token and its place),
+    and the loop sees a step's tokens only when it collects them."""
+    depth = 1
+
+    def __init__(self, engine, opts, stops, n):
+        self.e, self.stops = engine, set(stops)
+        self.next, self.made, self.limit, self.frozen = {}, {}, {}, {}
+        self.queue = []
+        self.launches = []
+
+    def _sample(self, slots, logits):
+        out = []
+        for s, row in zip(slots, logits):
+            tok = int(row.argmax())
+            out.append(tok)
+            if self.frozen[s]:
+                continue
+            self.made[s] += 1
+            self.next[s] = tok
+            if tok in self.stops or self.made[s] >= self.limit[s]:
+                self.frozen[s] = True
+        self.queue.append(out)
+
+    def start(self, slots, prompts, limits):
+        for s, l in zip(slots, limits):
+            self.made[s], self.limit[s], self.frozen[s] = 0, l, False
+        self._sample(slots, self.e.step(list(slots), [list(p) for p in prompts], None))
+
+    def launch(self, slots):
+        self.launches.append(list(slots))
+        live = [s for s in slots if not self.frozen[s]]
+        logits = torch.full((len(slots), self.e.vocab), -1.0)
+        if live:
+            got = self.e.step(live, [[self.next[s]] for s in live], None)
+            for s, row in zip(live, got):
+                logits[slots.index(s)] = row
+        self._sample(slots, logits)
+
+    def collect(self):
+        return self.queue.pop(0)
+
+
+def test_a_run_one_step_ahead_gives_the_same_results():
+    prompts = [[1], [30], [40, 41], [7]]
+    kw = dict(max_tokens=6, stop_token_ids=[4, 44])
+    want = run(ScriptedEngine(), prompts, **kw)
+    e = ScriptedEngine()
+    runs = []
+
+    def factory(engine, opts, stops, n):
+        runs.append(LaggingRun(engine, opts, stops, n))
+        return runs[-1]
+
+    got = generate(e, prompts, GenOptions(sampler=SamplerConfig.greedy(), **kw), run_factory=factory)
+    assert [(r.tokens, r.finish) for r in got] == [(r.tokens, r.finish) for r in want]
+    assert got[0].tokens == [2, 3] and got[0].finish == "stop" and got[2].tokens == [42, 43]
+    fed = [t for _, toks in e.steps[1:] for seq in toks for t in seq]
+    assert 4 not in fed and 44 not in fed, "a stop token is never fed, not even in the step launched ahead"
+    # sequence 0 stops at its third token: the step launched before the loop read that token
+    # still carries its slot (frozen), the one after does not
+    slot0 = e.opened[0]
+    assert [slot0 in l for l in runs[0].launches] == [True, True, True, False, False]
+    e.cache.check()
+    assert e.cache.slots.n_held == 0 and e.cache.pages.n_held == 0
+
+
+def test_a_run_ahead_launches_nothing_beyond_the_length_limits():
+    e = ScriptedEngine()
+    runs = []
+    res = generate(e, [[1, 2, 3], [10]], GenOptions(sampler=SamplerConfig.greedy(), max_tokens=4),
+                   run_factory=lambda eng, o, st, n: runs.append(LaggingRun(eng, o, st, n)) or runs[-1])
+    assert [r.tokens for r in res] == [[4, 5, 6, 7], [11, 12, 13, 14]]
+    assert len(runs[0].launches) == 3 and len(e.steps) == 4, "no step runs after the last token"
+
+
+def test_stop_tokens_of_the_model_end_a_sequence_without_being_asked_for():
+    e = ScriptedEngine()
+    e.spec = type("Spec", (), {"stop_token_ids": (5,)})()
+    res = run(e, [[1], [30]], max_tokens=8)
+    assert res[0].tokens == [2, 3, 4] and res[0].finish == "stop" and res[1].finish == "length"
+    res = run(e, [[1]], max_tokens=8, stop_token_ids=[3])
+    assert res[0].tokens == [2] and res[0].finish == "stop", "the caller's stop tokens are added to the model's"
+
+
+def test_kernel_status_is_checked_when_a_batch_has_drained():
+    e = ScriptedEngine()
+    calls = []
+    e.check_kernels = lambda: calls.append(1)
+    run(e, [[i] for i in range(5)], max_tokens=2, max_batch=2)
+    assert len(calls) == 3, "once per batch"

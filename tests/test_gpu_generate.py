@@ -10,7 +10,8 @@ import torch
 pytestmark = pytest.mark.gpu
 
 import wick_b200 as wick  # noqa: E402
-from helpers import CONFIGS, make_engine, model_dir, plain_model, random_tokens  # noqa: E402
+from helpers import (BF16_REL, CONFIGS, assert_logits_close, make_engine, model_dir, plain_model,  # noqa: E402
+                     random_tokens)
 from plain import qwen3_plain as P  # noqa: E402
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -22,7 +23,7 @@ STD = 0.08
 
 
 def test_greedy_generation_matches_the_plain_loop_config_a():
-    """BASELINE's tiny workload A: 3 prompts of 5/11/17 tokens, 8 greedy steps."""
+    """The tiny workload A: 3 prompts of 5/11/17 tokens, 8 greedy steps."""
     eng = make_engine("A", "float32", std=STD)
     cfg, w = plain_model("A", std=STD)
     prompts = [random_tokens(512, n, 60 + n) for n in (5, 11, 17)]
@@ -47,14 +48,30 @@ def test_greedy_with_stop_tokens_and_more_requests_than_a_batch_holds(dtype):
         assert [r.tokens for r in out] == want
         assert out[1].finish == "stop" and len(out[1].tokens) <= 4
     else:
-        # bfloat16 may pick another of two close candidates; the first tokens agree
-        assert sum(r.tokens[:2] == w_[:2] for r, w_ in zip(out, want)) >= len(want) - 1
+        # bfloat16 may pick another of two close candidates.  Every token it did pick must be
+        # one the plain implementation rates within the bfloat16 tolerance of its best, at the
+        # position where it was picked; and the engine's own logits along the generated
+        # sequence (fed again, one token at a time) must match the plain ones.
+        for p, r in zip(prompts, out):
+            seq = list(p) + r.tokens
+            ref = P.forward(cfg, w, seq) if len(seq) > len(p) else None
+            slot = eng.open_seq()
+            got = [eng.step([slot], [list(p)]).clone()] + [eng.step([slot], [[t]]).clone() for t in r.tokens[:-1]]
+            eng.close_seq(slot)
+            for i, t in enumerate(r.tokens):
+                row = ref[len(p) - 1 + i]
+                assert row[t] >= row.max() - BF16_REL * row.abs().max(), f"token {i} of prompt {len(p)}"
+                assert int(got[i][0].argmax()) == t or got[i][0][t] >= got[i][0].max() - 1e-3 * got[i][0].abs().max()
+            if r.tokens:
+                assert_logits_close(torch.cat(got), ref[len(p) - 1:len(p) - 1 + len(r.tokens)], dtype, "generated positions")
+            assert r.finish in ("stop", "length") and (r.finish == "length") == (len(r.tokens) == 10)
+            assert stop not in r.tokens
     eng.cache.check()
     assert eng.cache.pages.n_held == 0
 
 
 def test_temperature_sampling_given_the_engines_logits():
-    """BASELINE's tiny workload B: prompts 1/7/30/64, 12 steps at temperature 0.8
+    """The tiny workload B: prompts 1/7/30/64, 12 steps at temperature 0.8
     with a fixed seed.  The tokens must be the ones the plain sampler draws from
     the logits the engine produced (the sampler is tested apart from the model)."""
     eng = make_engine("B", "float32", std=STD)
@@ -106,3 +123,86 @@ def test_command_line_run_and_errors(tmp_path):
     r = subprocess.run(cmd + ["bench", d, "--prompt-len", "16", "-n", "4", "--batch", "2", "-q", "bf16"],
                        capture_output=True, text=True, env=env, timeout=600)
     assert r.returncode == 0 and "tok/s" in r.stdout and "ms/step" in r.stdout, r.stderr
+
+
+SAMPLERS = [wick.SamplerConfig.greedy(),
+            wick.SamplerConfig(temperature=0.8, seed=1234),
+            wick.SamplerConfig(temperature=0.9, top_k=0, top_p=1.0, seed=77),
+            wick.SamplerConfig(temperature=1.1, top_k=20, top_p=0.8, min_p=0.05, repetition_penalty=1.3, seed=5)]
+
+
+@pytest.mark.parametrize("name, dtype", [("A", "float32"), ("D", "bfloat16"), ("R", "bfloat16")])
+def test_a_batch_stepped_on_the_device_gives_the_tokens_of_the_stepwise_loop(name, dtype):
+    """The generation loop over a batch that is advanced on the device (sampled token, length,
+    finished flag, generators and seen tokens stay there; the host reads one step behind)
+    against the same loop taking one step at a time with the sampler on the host side: same
+    tokens and endings for every way of sampling, with stop tokens, with requests that end at
+    different times and with more requests than one batch holds.  (R has a vocabulary beyond
+    the selection kernel's 1,024 candidates: the draw over all tokens.)"""
+    vocab = CONFIGS[name]["vocab_size"]
+    eng = make_engine(name, dtype, std=STD, max_tokens=64 * 12)
+    prompts = [random_tokens(vocab, n, 300 + n) for n in (3, 70, 1, 18, 40, 9, 2)]
+    for k, cfg in enumerate(SAMPLERS):
+        base = wick.GenOptions(max_tokens=9, sampler=cfg, max_batch=4)
+        free = wick.generate(eng, prompts, base, sampler_factory=wick.Sampler)
+        stop = [free[1].tokens[3], free[4].tokens[0]]
+        opts = wick.GenOptions(max_tokens=9, sampler=cfg, max_batch=4, stop_token_ids=stop)
+        want = wick.generate(eng, prompts, opts, sampler_factory=wick.Sampler)
+        runs = []
+        begin = eng.begin_run
+        eng.begin_run = lambda *a, **kw: runs.append(begin(*a, **kw)) or runs[-1]
+        try:
+            got = wick.generate(eng, prompts, opts)
+        finally:
+            del eng.begin_run
+        assert [(r.tokens, r.finish) for r in got] == [(r.tokens, r.finish) for r in want], f"sampler {k}"
+        assert any(r.finish == "stop" for r in got) and any(r.finish == "length" for r in got)
+        assert len(runs) == 2, "two batches"
+        # a description goes to the device when the batch's composition changes, not every step
+        assert all(r.uploads <= 5 for r in runs), [r.uploads for r in runs]
+        eng.cache.check()
+        assert eng.cache.pages.n_held == 0 and eng.cache.slots.n_held == 0
+
+
+def test_steady_decoding_uploads_nothing():
+    eng = make_engine("D", "bfloat16", std=STD, max_tokens=64 * 16)
+    prompts = [random_tokens(640, n, 500 + n) for n in (30, 5, 11)]
+    runs = []
+    begin = eng.begin_run
+    eng.begin_run = lambda *a, **kw: runs.append(begin(*a, **kw)) or runs[-1]
+    out = wick.generate(eng, prompts, wick.GenOptions(max_tokens=40, sampler=wick.SamplerConfig.greedy()))
+    assert all(len(r.tokens) == 40 for r in out)
+    assert runs[0].uploads == 1, "39 decode steps of one composition: one description"
+    cfg, w = plain_model("D", std=STD)
+    for p, r in zip(prompts, out):
+        ref = P.forward(cfg, w, list(p) + r.tokens)
+        for i, t in enumerate(r.tokens):
+            row = ref[len(p) - 1 + i]
+            assert row[t] >= row.max() - BF16_REL * row.abs().max()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_models_own_stop_tokens_end_a_sequence(dtype):
+    """Config B names two end-of-sequence ids (7 and 9).  A prompt whose greedy continuation
+    under the plain implementation reaches one of them: the entry point and the command line
+    must stop there without being told any stop token."""
+    cfg, w = plain_model("B", std=STD)
+    p = random_tokens(1000, 4, 9058)             # (found by a search over seeds: reaches token 9 at its ninth token)
+    toks = P.greedy(cfg, w, p, 12)
+    assert any(t in (7, 9) for t in toks[1:]), "the prompt no longer reaches an end-of-sequence id: search again"
+    cut = next(i for i, t in enumerate(toks) if t in (7, 9))
+    want = P.greedy(cfg, w, p, 12, stop=(7, 9))
+    assert want == toks[:cut]
+    eng = make_engine("B", dtype, std=STD)
+    out = wick.generate(eng, [p], wick.GenOptions(max_tokens=12, sampler=wick.SamplerConfig.greedy()))[0]
+    if dtype == "float32":
+        assert out.tokens == want and out.finish == "stop"
+        env = dict(os.environ, PYTHONPATH=ROOT)
+        r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "wick"), "run", model_dir("B", std=STD), "--ids",
+                            ",".join(map(str, p)), "-n", "12", "-t", "0", "-q", "f32"], capture_output=True, text=True,
+                           env=env, timeout=600)
+        assert r.returncode == 0, r.stderr
+        assert json.loads(r.stdout.strip().splitlines()[0]) == want and "Stop" in r.stderr
+    else:
+        assert 7 not in out.tokens and 9 not in out.tokens
+        assert out.finish == "stop" or len(out.tokens) == 12

@@ -161,8 +161,8 @@ def cmd_run(a: Args) -> None:
     per_seq = [min(a.context, len(p) + a.max_tokens) for p in a.prompts]
     need = sum(sorted(((n + 63) // 64 * 64 for n in per_seq), reverse=True)[:batch])
     eng = _load(a, max(need, 64))
-    stops = list(eng.spec.stop_token_ids) + a.stop_ids
-    opts = wick.GenOptions(max_tokens=a.max_tokens, sampler=a.sampler, stop_token_ids=stops, context=a.context,
+    # (the model's own end-of-sequence ids are added by the generation loop)
+    opts = wick.GenOptions(max_tokens=a.max_tokens, sampler=a.sampler, stop_token_ids=a.stop_ids, context=a.context,
                            max_batch=batch)
     res = wick.generate(eng, a.prompts, opts)
     for r in res:

@@ -65,7 +65,8 @@ class StepBatch:
     """
 
     def __init__(self, layout: BatchLayout, dev: torch.Tensor, *, q_lens: Sequence[int],
-                 starts: Sequence[int], host: Optional[np.ndarray] = None):
+                 starts: Sequence[int], host: Optional[np.ndarray] = None, workspace=None,
+                 kv_bound: Optional[int] = None):
         L = layout
         self.layout = L
         self.buffer = dev
@@ -77,6 +78,11 @@ class StepBatch:
         self.max_kv_len = max((s + q for s, q in zip(self.starts, self.q_lens)), default=0)
         self.is_decode = self.max_q_len == 1 and self.n_tokens == self.n_seqs
         self.host = host
+        # Scratch buffers that outlive the step (an object with ``get(name, numel, dtype)``),
+        # and the number of cached positions that kernels size their work by: the longest
+        # sequence of this step, or more (a captured step is sized for its page table).
+        self.workspace = workspace
+        self.kv_bound = self.max_kv_len if kv_bound is None else kv_bound
         v = lambda off, n: dev[off:off + n]
         self.tokens = v(L.tokens, L.n_tokens)
         self.positions = v(L.positions, L.n_tokens)

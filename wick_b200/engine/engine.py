@@ -89,6 +89,10 @@ class _DecodeGraph:
         self.n_pad, self.table_width = n_pad, table_width
         self.layout = BatchLayout(n_pad, n_pad, table_width, n_pad, n_pad)
         self.buffer: Optional[torch.Tensor] = None
+        self.batch: Optional[StepBatch] = None
+        # What a batch that decodes on the device last wrote into the buffer (its slots and
+        # how many pages each held); None after anyone else filled it.
+        self.composition: Optional[tuple] = None
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.logits: Optional[torch.Tensor] = None
 
@@ -113,6 +117,12 @@ class Engine:
         self.use_graphs = use_graphs
         self._graphs: Dict[Tuple[int, int], _DecodeGraph] = {}
         self._steps_since_check = 0
+        # One record per cache slot on the device (length, next token, finished, ...): what a
+        # batch that decodes without the host in between is advanced by.  Slot 0 (padding) is
+        # finished for ever.
+        self.seq_state = torch.zeros((self.cache.max_seqs + 1, ops.SEQ_STATE_WORDS), dtype=torch.int32,
+                                     device=self.device)
+        self.seq_state[0, ops.SEQ_FINISHED] = 1
 
     # ---- construction ----------------------------------------------------
     @classmethod
@@ -152,6 +162,12 @@ class Engine:
     def seq_len(self, slot: int) -> int:
         return self.cache.length(slot)
 
+    def begin_run(self, sampler, stop_token_ids=()):
+        """A batch of sequences that start together and then decode on the device: see
+        :class:`~wick_b200.engine.run.DeviceRun`."""
+        from .run import DeviceRun
+        return DeviceRun(self, sampler, stop_token_ids)
+
     # ---- the step ------------------------------------------------------------
     def _check(self, slots, tokens, want) -> None:
         if not (len(slots) == len(tokens) == len(want)):
@@ -176,7 +192,11 @@ class Engine:
 
         want[b]: indices into tokens[b] whose logits are returned (default: the
         last one).  Returns float32 [sum(len(want[b])), vocab], rows in the order
-        of the sequences and of ``want``."""
+        of the sequences and of ``want``.
+
+        The result of a captured decode step (one token per sequence, graphs on) is a
+        view of that captured step's output buffer: it is valid until the next step of
+        the same batch size runs, so copy it (``.clone()``) to keep it longer."""
         if want is None:
             want = [[len(t) - 1] for t in tokens]
         self._check(slots, tokens, want)
@@ -205,6 +225,9 @@ class Engine:
         return dev, arr
 
     def _step_eager(self, slots, tokens, want, starts, q_lens) -> torch.Tensor:
+        return self._forward_eager(slots, tokens, want, starts, q_lens)[0]
+
+    def _forward_eager(self, slots, tokens, want, starts, q_lens) -> Tuple[torch.Tensor, StepBatch]:
         cache = self.cache
         B = len(slots)
         kv_lens = [s + q for s, q in zip(starts, q_lens)]
@@ -212,15 +235,17 @@ class Engine:
         layout = BatchLayout(B, sum(q_lens), width, sum(len(w) for w in want), n_q_tiles(q_lens))
         pages = [cache.pages_of(s)[:(k + PAGE - 1) // PAGE] for s, k in zip(slots, kv_lens)]
         dev, _ = self._upload(layout, None, tokens=tokens, starts=starts, slots=slots, pages=pages, want=want)
-        batch = StepBatch(layout, dev, q_lens=q_lens, starts=starts)
-        batch.workspace = self.workspace
-        batch.kv_bound = batch.max_kv_len
+        batch = StepBatch(layout, dev, q_lens=q_lens, starts=starts, workspace=self.workspace)
         with ops.stream_scope():
             logits = self.model.forward(batch, cache)
+        self._count_step()
+        return logits, batch
+
+    def _count_step(self) -> None:
+        """Every 64 steps (replayed ones too) the kernels' status word is read."""
         self._steps_since_check += 1
         if self._steps_since_check >= 64:
             self.check_kernels()
-        return logits
 
     # ---- captured decode -------------------------------------------------------
     @staticmethod
@@ -230,11 +255,10 @@ class Engine:
             b *= 2
         return b
 
-    def _step_graph(self, slots, tokens, want, starts) -> torch.Tensor:
-        cache = self.cache
-        B = len(slots)
-        n_pad = self._bucket(B)
-        max_pages = max((s + 1 + PAGE - 1) // PAGE for s in starts)
+    def _decode_graph(self, n_seqs: int, max_pages: int) -> _DecodeGraph:
+        """The captured step for ``n_seqs`` sequences (padded to a power of two) whose page
+        tables hold up to ``max_pages`` pages (padded to 8, 16, 32 ...); captured on first use."""
+        n_pad = self._bucket(n_seqs)
         width = 8
         while width < max_pages:
             width *= 2
@@ -243,22 +267,33 @@ class Engine:
         if g is None:
             g = self._graphs[key] = _DecodeGraph(n_pad, width)
             g.buffer = torch.zeros(g.layout.size, dtype=torch.int32, device=self.device)
-        pad = n_pad - B
-        # Padded entries: one token (id 0) at position 0 of the reserved page 0 / slot 0.
-        f_tokens = [list(t) for t in tokens] + [[0]] * pad
-        f_starts = list(starts) + [0] * pad
-        f_slots = list(slots) + [0] * pad
-        f_pages = [cache.pages_of(s)[:(st + 1 + PAGE - 1) // PAGE] for s, st in zip(slots, starts)] + [[0]] * pad
-        f_want = [[0]] * n_pad            # the graph always computes every row's logits
+            g.batch = StepBatch(g.layout, g.buffer, q_lens=[1] * n_pad, starts=[0] * n_pad, workspace=self.workspace,
+                                kv_bound=width * PAGE)
         if g.graph is None:
             # Capture (and its warm-up run) on a batch of padding entries only, so
             # that no live sequence's cache or state is touched twice.
             self._upload(g.layout, g.buffer, tokens=[[0]] * n_pad, starts=[0] * n_pad, slots=[0] * n_pad,
-                         pages=[[0]] * n_pad, want=f_want)
+                         pages=[[0]] * n_pad, want=[[0]] * n_pad)
             self._capture(g)
-        self._upload(g.layout, g.buffer, tokens=f_tokens, starts=f_starts, slots=f_slots, pages=f_pages, want=f_want)
+        return g
+
+    def _fill_graph_batch(self, g: _DecodeGraph, slots, tokens, starts) -> None:
+        """The description of a decode step of ``slots`` into the captured step's buffer;
+        padded entries are one token (id 0) at position 0 of the reserved page 0 / slot 0."""
+        cache = self.cache
+        pad = g.n_pad - len(slots)
+        f_pages = [cache.pages_of(s)[:g.table_width] for s in slots] + [[0]] * pad
+        self._upload(g.layout, g.buffer, tokens=[list(t) for t in tokens] + [[0]] * pad, starts=list(starts) + [0] * pad,
+                     slots=list(slots) + [0] * pad, pages=f_pages, want=[[0]] * g.n_pad)
+        g.composition = None
+
+    def _step_graph(self, slots, tokens, want, starts) -> torch.Tensor:
+        B = len(slots)
+        g = self._decode_graph(B, max((s + 1 + PAGE - 1) // PAGE for s in starts))
+        self._fill_graph_batch(g, slots, tokens, starts)
         g.graph.replay()
         ops.launches[0] += g.kernels
+        self._count_step()
         rows = [b for b in range(B) for _ in want[b]]
         if rows == list(range(B)):
             return g.logits[:B]
@@ -267,15 +302,10 @@ class Engine:
         return g.logits[torch.tensor(rows, device=self.device)]
 
     def _capture(self, g: _DecodeGraph) -> None:
-        q_lens = [1] * g.n_pad
-        kv_bound = g.table_width * PAGE
-
         def run():
-            batch = StepBatch(g.layout, g.buffer, q_lens=q_lens, starts=[0] * g.n_pad)
-            batch.workspace = self.workspace
-            batch.kv_bound = kv_bound
+            g.batch.memo.clear()
             with ops.stream_scope():                # (entered on the stream that runs or captures the step)
-                return self.model.forward(batch, self.cache)
+                return self.model.forward(g.batch, self.cache)
 
         # Warm-up outside capture (compiles/loads kernels, grows scratch buffers).
         s = torch.cuda.Stream()

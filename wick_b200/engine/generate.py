@@ -20,11 +20,13 @@ without a GPU.
 """
 from __future__ import annotations
 
+import collections
 import dataclasses
 import time
 from typing import Callable, List, Optional, Sequence
 
 from ..sampling.sampler import Sampler, SamplerConfig
+from .run import StepRun
 
 PAGE = 64
 
@@ -54,12 +56,14 @@ class GenResult:
 
 
 class _Live:
-    __slots__ = ("req", "slot", "prompt", "out", "limit", "next_token", "t_start", "t_prompt")
+    __slots__ = ("req", "slot", "prompt", "out", "limit", "launched", "done", "t_prompt")
 
     def __init__(self, req, slot, prompt, limit):
         self.req, self.slot, self.prompt, self.limit = req, slot, prompt, limit
         self.out: List[int] = []
-        self.next_token = -1
+        self.launched = 0          # steps launched that sample a token for this sequence
+        self.done = False
+        self.t_prompt = 0.0
 
 
 def _pages(n: int) -> int:
@@ -82,15 +86,30 @@ def plan_batch(waiting: Sequence[int], prompt_lens: Sequence[int], limits: Seque
     return chosen
 
 
+def stop_set(engine, opts: GenOptions) -> set:
+    """The tokens that end a sequence: the model's own (its configuration's end-of-sequence
+    ids, as wick's engine collects them, engine.rs:41-51) and the caller's."""
+    own = getattr(getattr(engine, "spec", None), "stop_token_ids", ()) or ()
+    return set(int(t) for t in own) | set(int(t) for t in opts.stop_token_ids)
+
+
 def generate(engine, prompts: Sequence[Sequence[int]], opts: Optional[GenOptions] = None,
              sampler_factory: Optional[Callable[[SamplerConfig, int], object]] = None,
-             on_step: Optional[Callable[[int, List[int]], None]] = None) -> List[GenResult]:
+             on_step: Optional[Callable[[int, List[int]], None]] = None,
+             run_factory: Optional[Callable[[object, GenOptions, set, int], object]] = None) -> List[GenResult]:
     """Generate a continuation for every prompt; results in the prompts' order.
 
-    engine: anything with ``open_seq()``, ``close_seq(slot)``, ``step(slots,
-    tokens, want) -> logits`` and a ``cache`` that tells free pages and slots."""
+    engine: anything with ``open_seq()``, ``close_seq(slot)``, a ``cache`` that tells free
+    pages and slots, and either ``begin_run(sampler_config, stop_ids)`` (a batch that is
+    stepped on the device, see ``engine/run.py``) or ``step(slots, tokens, want) -> logits``
+    (then, or when ``sampler_factory`` is given, one step at a time with a sampler on this
+    side).  ``run_factory(engine, opts, stops, n)`` overrides the choice.
+
+    A batch that is stepped on the device is one step ahead of what this loop has read: a
+    sequence that samples a stop token rides along, frozen, in the step that was launched
+    before the loop learned of it; that step changes nothing and its token is dropped."""
     opts = opts or GenOptions()
-    stops = set(int(t) for t in opts.stop_token_ids)
+    stops = stop_set(engine, opts)
     n = len(prompts)
     context = min(opts.context, getattr(engine.cache, "max_position", None) or opts.context)
     limits: List[int] = []
@@ -102,8 +121,14 @@ def generate(engine, prompts: Sequence[Sequence[int]], opts: Optional[GenOptions
         limits.append(min(opts.max_tokens, context - len(p)))
     results: List[Optional[GenResult]] = [None] * n
     waiting = list(range(n))
-    make_sampler = sampler_factory or (lambda cfg, k: Sampler(cfg, k))
-    needs_history = opts.sampler.repetition_penalty != 1.0
+
+    def make_run(k: int):
+        if run_factory is not None:
+            return run_factory(engine, opts, stops, k)
+        if sampler_factory is None and hasattr(engine, "begin_run"):
+            return engine.begin_run(opts.sampler, stops)
+        make_sampler = sampler_factory or (lambda cfg, m: Sampler(cfg, m))
+        return StepRun(engine, make_sampler(opts.sampler, k), opts.sampler.repetition_penalty != 1.0)
 
     while waiting:
         cache = engine.cache
@@ -116,56 +141,62 @@ def generate(engine, prompts: Sequence[Sequence[int]], opts: Optional[GenOptions
         waiting = waiting[len(chosen):]
         live: List[_Live] = []
         for r in chosen:
+            if limits[r] == 0:                         # nothing to generate: no slot, no step
+                results[r] = GenResult([], len(prompts[r]), "length")
+                continue
             slot = engine.open_seq()
             cache.reserve(slot, len(prompts[r]) + limits[r])
             live.append(_Live(r, slot, list(prompts[r]), limits[r]))
-        sampler = make_sampler(opts.sampler, len(live))
-        index = {id(s): i for i, s in enumerate(live)}
-
+        if not live:
+            continue
+        run = make_run(len(live))
         t0 = time.perf_counter()
-        feed = [s.prompt for s in live]
-        first = True
+        run.start([s.slot for s in live], [s.prompt for s in live], [s.limit for s in live])
+        for s in live:
+            s.launched = 1
+        pending = collections.deque([list(live)])      # the sequences of each step launched and not yet read
+        t1 = t0
         step_no = 0
-        while live:
-            # Sequences with a zero limit need no logits at all.
-            active = [s for s in live if s.limit > 0]
-            for s in live:
-                if s.limit == 0:
-                    results[s.req] = GenResult([], len(s.prompt), "length")
-                    engine.close_seq(s.slot)
-            if not active:
+        while True:
+            # Launch ahead: a step for every sequence that is not known to be finished and that
+            # its limit allows another token.  (None of them: nothing runs after the last token.)
+            while len(pending) < run.depth + 1:
+                rows = [s for s in live if not s.done and s.launched < s.limit]
+                if not rows:
+                    break
+                run.launch([s.slot for s in rows])
+                for s in rows:
+                    s.launched += 1
+                pending.append(rows)
+            if not pending:
                 break
-            if len(active) != len(live):
-                feed = [f for f, s in zip(feed, live) if s.limit > 0]
-                live = active
-            logits = engine.step([s.slot for s in live], feed, [[len(f) - 1] for f in feed])
-            hist = [s.prompt + s.out for s in live] if needs_history else None
-            toks = sampler.sample(logits, [index[id(s)] for s in live], hist)
+            rows = pending.popleft()
+            toks = run.collect()
             now = time.perf_counter()
-            if first:
-                for s in live:
+            if step_no == 0:
+                for s in rows:
                     s.t_prompt = (now - t0) * 1e3
                 t1 = now
-                first = False
-            nxt: List[_Live] = []
-            for s, tok in zip(live, toks):
+            for s, tok in zip(rows, toks):
+                if s.done:
+                    continue                           # it rode along after its end
                 tok = int(tok)
-                done = None
+                finish = None
                 if tok in stops:
-                    done = "stop"
+                    finish = "stop"
                 else:
                     s.out.append(tok)
                     if len(s.out) >= s.limit:
-                        done = "length"
-                if done:
-                    results[s.req] = GenResult(s.out, len(s.prompt), done, s.t_prompt, (now - t1) * 1e3)
+                        finish = "length"
+                if finish:
+                    s.done = True
+                    results[s.req] = GenResult(s.out, len(s.prompt), finish, s.t_prompt, (now - t1) * 1e3)
                     engine.close_seq(s.slot)
-                else:
-                    s.next_token = tok
-                    nxt.append(s)
-            live = nxt
-            feed = [[s.next_token] for s in live]
+            live = [s for s in live if not s.done]
             step_no += 1
             if on_step is not None:
                 on_step(step_no, [s.req for s in live])
+        check = getattr(engine, "check_kernels", None)
+        if check is not None:
+            check()                                    # a kernel that gave up a wait must not go unnoticed
     return results  # type: ignore[return-value]

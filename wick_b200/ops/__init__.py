@@ -73,10 +73,13 @@ _libs: Dict[str, _Lib] = {}
 launches = [0]
 
 
+CORE_SOURCES = ["core.cu", "sample.cu", "state.cu"]
+
+
 def _core() -> _Lib:
     lib = _libs.get("core")
     if lib is None:
-        lib = _libs["core"] = _Lib("wick_core", ["core.cu", "sample.cu"])
+        lib = _libs["core"] = _Lib("wick_core", CORE_SOURCES)
     return lib
 
 
@@ -526,7 +529,7 @@ def top_k(logits: torch.Tensor, k: int) -> Tuple[torch.Tensor, torch.Tensor]:
 
 
 def pick_sorted(vals: torch.Tensor, idx: torch.Tensor, uniforms: torch.Tensor, temperature: float, min_p: float,
-                top_p: float) -> torch.Tensor:
+                top_p: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One token per row from candidates sorted by logit (descending): the
     probabilities at ``temperature``, the min-p and top-p cuts and the draw with
     the row's uniform number, as ``sampling.sampler.pick_from_sorted`` does them
@@ -537,7 +540,9 @@ def pick_sorted(vals: torch.Tensor, idx: torch.Tensor, uniforms: torch.Tensor, t
     _cuda("uniforms", uniforms, torch.float32, (rows,))
     _need(temperature > 0.0, "pick_sorted needs a temperature above 0")
     probs = torch.empty_like(vals)
-    out = torch.empty(rows, dtype=torch.int32, device=vals.device)
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=vals.device)
+    _cuda("out", out, torch.int32, (rows,))
     _core().call("wick_pick_sorted", "pppppiifffp", _p(vals), _p(idx), _p(uniforms), _p(probs), _p(out), rows, k,
                  float(temperature), float(min_p), float(top_p), _stream())
     return out
@@ -560,3 +565,94 @@ def repetition_penalty(logits: torch.Tensor, histories, penalty: float) -> torch
     _core().call("wick_repetition_penalty", "pppiifp", _p(logits), _p(dev[0]), _p(dev[1]), len(t), vocab,
                  float(penalty), _stream())
     return logits
+
+
+# ---------------------------------------------------------------------------
+# The per-sequence state record on the device (csrc/state.cu) and the kernels that
+# move a batch from one decode step to the next without the host.
+SEQ_STATE_WORDS = 8
+SEQ_LENGTH, SEQ_NEXT, SEQ_FINISHED, SEQ_GENERATED, SEQ_LIMIT, SEQ_ROW = range(6)
+
+
+def seq_state_set(state: torch.Tensor, slots: torch.Tensor, values: torch.Tensor) -> None:
+    """state[slots[i]] = values[i] (int32 records of SEQ_STATE_WORDS words)."""
+    _cuda("state", state, torch.int32)
+    n = slots.numel()
+    _cuda("slots", slots, torch.int32, (n,))
+    _cuda("values", values, torch.int32, (n, SEQ_STATE_WORDS))
+    _need(state.dim() == 2 and state.shape[1] == SEQ_STATE_WORDS, "state must be [slots, 8]")
+    _core().call("wick_seq_state_set", "pppip", _p(state), _p(slots), _p(values), n, _stream())
+
+
+def step_prepare(state: torch.Tensor, slots: torch.Tensor, tokens: torch.Tensor, positions: torch.Tensor,
+                 start: torch.Tensor, kv_len: torch.Tensor) -> None:
+    """The fields of a decode step from the sequences' records: the token sampled last, its
+    position, and the cached length before and after the step."""
+    n = slots.numel()
+    _cuda("state", state, torch.int32)
+    for nm, t in (("slots", slots), ("tokens", tokens), ("positions", positions), ("start", start), ("kv_len", kv_len)):
+        _cuda(nm, t, torch.int32, (n,))
+    _core().call("wick_step_prepare", "ppppppip", _p(state), _p(slots), _p(tokens), _p(positions), _p(start), _p(kv_len),
+                 n, _stream())
+
+
+def step_advance(state: torch.Tensor, slots: torch.Tensor, ids: torch.Tensor, kv_len: torch.Tensor,
+                 stops: Optional[torch.Tensor], seen: Optional[torch.Tensor], vocab: int) -> None:
+    """After sampling: every running sequence of the step takes its sampled token (ids[i]) as
+    its next one and its new length, or is marked finished (a stop token, or its limit).
+    ids has one element more than there are rows; it receives the kernels' status word."""
+    n = slots.numel()
+    _cuda("state", state, torch.int32)
+    _cuda("slots", slots, torch.int32, (n,))
+    _cuda("ids", ids, torch.int32, (n + 1,))
+    _cuda("kv_len", kv_len, torch.int32, (n,))
+    n_stops = 0
+    if stops is not None and stops.numel():
+        _cuda("stops", stops, torch.int32)
+        n_stops = stops.numel()
+    if seen is not None:
+        _cuda("seen", seen, torch.uint8)
+        _need(seen.dim() == 2 and seen.shape[1] == vocab, f"seen must be [rows, {vocab}]")
+    _core().call("wick_step_advance", "pppppipipip", _p(state), _p(slots), _p(ids), _p(kv_len),
+                 _p(stops) if n_stops else None, n_stops, _p(seen), vocab, _p(status_tensor(state.device)), n, _stream())
+
+
+def rng_uniforms(rng: torch.Tensor, state: torch.Tensor, slots: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One uniform number in [0, 1) per row from the generator (xoshiro256**, int64 [rows of the
+    batch, 4]) of the row's sequence; the generators of running sequences move on."""
+    n = slots.numel()
+    _cuda("rng", rng, torch.int64)
+    _need(rng.dim() == 2 and rng.shape[1] == 4, "rng must be [rows, 4]")
+    _cuda("state", state, torch.int32)
+    _cuda("slots", slots, torch.int32, (n,))
+    if out is None:
+        out = torch.empty(n, dtype=torch.float32, device=state.device)
+    _cuda("out", out, torch.float32, (n,))
+    _core().call("wick_rng_uniforms", "ppppip", _p(rng), _p(state), _p(slots), _p(out), n, _stream())
+    return out
+
+
+def seen_prompt(seen: torch.Tensor, state: torch.Tensor, slots: torch.Tensor, tokens: torch.Tensor,
+                seq_of_token: torch.Tensor) -> None:
+    """Mark a prompt step's tokens as seen in their sequences' rows of ``seen`` (uint8 [rows, vocab])."""
+    _cuda("seen", seen, torch.uint8)
+    _cuda("state", state, torch.int32)
+    _cuda("slots", slots, torch.int32)
+    n = tokens.numel()
+    _cuda("tokens", tokens, torch.int32, (n,))
+    _cuda("seq_of_token", seq_of_token, torch.int32, (n,))
+    _core().call("wick_seen_prompt", "pippppip", _p(seen), seen.shape[1], _p(state), _p(slots), _p(tokens),
+                 _p(seq_of_token), n, _stream())
+
+
+def penalty_seen(logits: torch.Tensor, seen: torch.Tensor, state: torch.Tensor, slots: torch.Tensor, penalty: float) -> None:
+    """In place: the logit of every token seen in the row's sequence is divided by ``penalty``
+    if positive, multiplied otherwise."""
+    _cuda("logits", logits, torch.float32)
+    rows, vocab = logits.shape
+    _cuda("seen", seen, torch.uint8)
+    _need(seen.dim() == 2 and seen.shape[1] == vocab, f"seen must be [rows, {vocab}]")
+    _cuda("state", state, torch.int32)
+    _cuda("slots", slots, torch.int32, (rows,))
+    _core().call("wick_penalty_seen", "ppippfip", _p(logits), _p(seen), vocab, _p(state), _p(slots), float(penalty), rows,
+                 _stream())

@@ -109,8 +109,42 @@ def pick_from_sorted(vals: np.ndarray, idx: np.ndarray, cfg: SamplerConfig, rng:
     return int(idx[keep - 1])
 
 
+def rng_state(seed: int) -> List[int]:
+    """The four 64-bit words of a freshly seeded generator, as signed integers (the form an
+    int64 tensor holds them in for the device's generator kernel)."""
+    return [w - (1 << 64) if w >= (1 << 63) else w for w in Rng(seed).s]
+
+
+def sample_on_device(cfg: SamplerConfig, logits: torch.Tensor, uniforms, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token per row of float32 ``logits`` [rows, vocab] on the device, as int32 [rows] on
+    the device; nothing is copied to the host.  ``uniforms`` is a function that returns this
+    step's uniform numbers (float32 [rows] on the device); it is called only if a draw is made.
+    A repetition penalty is applied by the caller beforehand.  ``out``: where to write (int32 [rows]).
+
+    Where every token is a candidate (``top_k`` 0, no min-p, no top-p) and the vocabulary is
+    larger than the selection kernel's 1,024 candidates, the draw walks the candidates in the
+    order of their ids, not sorted by logit as sampler.rs:116-125 does: the same distribution,
+    but for one uniform number another token than the reference picks."""
+    from .. import ops
+    rows, vocab = logits.shape
+    if cfg.temperature <= 0.0:
+        return ops.argmax(logits, out)
+    k = vocab if cfg.top_k == 0 else min(cfg.top_k, vocab)
+    if k == vocab and cfg.top_p >= 1.0 and cfg.min_p <= 0.0 and vocab > Sampler.DEVICE_TOP_K:
+        return ops.sample_temperature(logits, cfg.temperature, uniforms(), out)
+    if k <= Sampler.DEVICE_TOP_K:
+        vals, idx = ops.top_k(logits, k)
+    else:
+        # More candidates than the selection kernel takes (rare): a library sort, ties by index.
+        vals, order = torch.sort(logits, dim=1, descending=True, stable=True)
+        vals, idx = vals[:, :k].contiguous(), order[:, :k].to(torch.int32).contiguous()
+    return ops.pick_sorted(vals, idx, uniforms(), cfg.temperature, cfg.min_p, cfg.top_p, out)
+
+
 class Sampler:
-    """Samples one token per row of a batch of logits; one :class:`Rng` per sequence."""
+    """Samples one token per row of a batch of logits; one :class:`Rng` per sequence.  (The
+    form for callers that hold the logits of a step in their hands; a batch that decodes
+    without the host in between keeps its generators on the device instead.)"""
 
     DEVICE_TOP_K = 1024
 
@@ -133,17 +167,9 @@ class Sampler:
                 raise ValueError("a repetition penalty needs the sequences' tokens")
             logits = logits.clone()
             ops.repetition_penalty(logits, histories, cfg.repetition_penalty)
-        if cfg.temperature <= 0.0:
-            return ops.argmax(logits).tolist()
-        k = vocab if cfg.top_k == 0 else min(cfg.top_k, vocab)
-        if k == vocab and cfg.top_p >= 1.0 and cfg.min_p <= 0.0 and vocab > self.DEVICE_TOP_K:
+
+        def uniforms():
             u = torch.tensor([self.rngs[s].next_f32() for s in seq_ids], dtype=torch.float32)
-            return ops.sample_temperature(logits, cfg.temperature, u.to(logits.device)).tolist()
-        if k <= self.DEVICE_TOP_K:
-            vals, idx = ops.top_k(logits, k)
-        else:
-            # More candidates than the selection kernel takes (rare): a library sort, ties by index.
-            vals, order = torch.sort(logits, dim=1, descending=True, stable=True)
-            vals, idx = vals[:, :k].contiguous(), order[:, :k].to(torch.int32).contiguous()
-        u = torch.tensor([self.rngs[s].next_f32() for s in seq_ids], dtype=torch.float32)
-        return ops.pick_sorted(vals, idx, u.to(logits.device), cfg.temperature, cfg.min_p, cfg.top_p).tolist()
+            return u.to(logits.device)
+
+        return sample_on_device(cfg, logits, uniforms).tolist()
