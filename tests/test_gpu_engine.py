@@ -392,3 +392,73 @@ def test_batch_composition_changes_no_bit_with_tensor_core_attention(name, dtype
     assert_logits_close(outs[24], plain_logits(name, seqs[0])[-4:], dtype, "batched decode")
     assert torch.equal(outs[1], outs[3]), "alone and among 3"
     assert torch.equal(outs[1], outs[24]), "alone and among 24"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_a_shared_prefix_is_kept_and_only_the_rest_runs(name, dtype):
+    """Prefix reuse (wick src/engine.rs:127-132): a sequence is cut back to the 70 tokens its
+    next prompt shares with the last one (inside its second page), the pages beyond are given
+    back and poisoned, and only the new prompt's remaining tokens run."""
+    eng = make_engine(name, dtype, max_tokens=1024)
+    poison_all(eng)
+    first = random_tokens(vocab_of(name), 200, 61)
+    second = first[:70] + random_tokens(vocab_of(name), 90, 62)
+    s = eng.open_seq()
+    eng.step([s], [first], [[]])
+    for t in random_tokens(vocab_of(name), 3, 63):
+        eng.step([s], [[t]])
+    held = eng.cache.pages.n_held
+    eng.truncate_seq(s, 70)
+    assert eng.seq_len(s) == 70 and eng.cache.pages.n_held == 2 < held
+    poison_free_pages(eng)
+    got = eng.step([s], [second[70:]], [list(range(90))]).clone()
+    ref = plain_logits(name, second)
+    assert_logits_close(got, ref[70:], dtype, f"{name} after a cut to 70 tokens")
+    got = eng.step([s], [[5]]).clone()
+    assert_logits_close(got, plain_logits(name, second + [5])[-1:], dtype, f"{name} decode after the cut")
+    with pytest.raises(ValueError, match="cannot truncate"):
+        eng.truncate_seq(s, 500)
+    eng.close_seq(s)
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_tensors_by_name_come_back_as_the_checkpoint_stores_them(dtype):
+    """Fused and tiled matrices are split and put back row by row: every tensor of the folder
+    is found under its name with its values (bfloat16 values are exact in float32)."""
+    from helpers import model_dir
+    from plain import qwen3_plain as P
+    for name in ("B", "D"):
+        eng = make_engine(name, dtype)
+        _, stored = P.read_model_dir(model_dir(name))
+        held = eng.model.tensors()
+        assert set(held) == set(stored)
+        for k, t in stored.items():
+            assert torch.equal(held[k].float().cpu(), t), k
+        assert torch.equal(eng.model.tensor("model.layers.1.self_attn.k_proj.weight").float().cpu(),
+                           stored["model.layers.1.self_attn.k_proj.weight"])
+        with pytest.raises(KeyError):
+            eng.model.tensor("model.layers.1.self_attn.nothing")
+
+
+def test_four_layers_at_the_real_sizes_of_qwen3_8b_in_float32():
+    """Four layers with the widths of Qwen3-8B and its full vocabulary of 151,936, random
+    float32 weights drawn on the device and handed to the plain implementation by tensor name:
+    a 300-token prompt and 8 decoded tokens, every wanted row within 1e-4."""
+    from plain import qwen3_plain as P
+    j = dict(CONFIGS["R"], num_hidden_layers=4, vocab_size=151936)
+    cfg = wick.config_from_json(j)
+    eng = wick.Engine.from_config(cfg, seed=5, dtype="float32", max_tokens=512)
+    w = {k: t.cpu() for k, t in eng.model.tensors().items()}
+    toks = random_tokens(151936, 308, 77)
+    ref = P.forward(P.plain_config(j), w, toks)
+    del w
+    s = eng.open_seq()
+    got = [eng.step([s], [toks[:300]], [[0, 150, 299]]).clone()]
+    for t in toks[300:]:
+        got.append(eng.step([s], [[t]]).clone())
+    eng.close_seq(s)
+    want = torch.cat([ref[[0, 150, 299]], ref[300:]])
+    assert_logits_close(torch.cat(got), want, "float32", "four real layers")
+    eng.check_kernels()

@@ -44,3 +44,11 @@ def test_how_a_plan_cuts_the_inner_dimension_at_the_sizes_of_qwen3_8b():
     assert [qkv.prompt_splits(t) for t in (256, 512, 2048)] == [2, 1, 1]
     assert gate_up.prompt_splits(256) == 1 and gate_up.mid_splits(100) == 1, "a gated pair has no partial sums"
     assert gate_up.pair_offset == 1024 and gate_up.n_out == 1024
+
+
+def test_unpack_gives_the_matrix_back():
+    from wick_b200.ops.gemm_tc import unpack
+    torch.manual_seed(2)
+    for rows, k, gated in [(300, 200, False), (2 * 130, 72, True), (128, 64, False), (2 * 128, 4096, True)]:
+        w = torch.randn(rows, k).bfloat16()
+        assert torch.equal(unpack(pack(w, gated), rows, k, gated), w)

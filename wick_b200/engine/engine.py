@@ -162,6 +162,13 @@ class Engine:
     def seq_len(self, slot: int) -> int:
         return self.cache.length(slot)
 
+    def truncate_seq(self, slot: int, length: int) -> None:
+        """Forget what the sequence holds from position ``length`` on, so that its next step
+        continues from there: a new prompt that shares its first ``length`` tokens with the
+        last one runs only the rest (wick src/engine.rs:127-132 keeps the common prefix of
+        consecutive prompts in the same way).  Pages beyond the new length are given back."""
+        self.cache.truncate(slot, length)
+
     def begin_run(self, sampler, stop_token_ids=()):
         """A batch of sequences that start together and then decode on the device: see
         :class:`~wick_b200.engine.run.DeviceRun`."""

@@ -57,6 +57,27 @@ class Model:
                 table[prefix + ts.name] = ts
         return table
 
+    def tensor(self, name: str) -> torch.Tensor:
+        """The loaded tensor of this full name, in the layout a checkpoint stores it in
+        (fused matrices split again, tiled ones put back row by row)."""
+        for prefix, part in self._places():
+            if name.startswith(prefix):
+                t = part.tensor(name[len(prefix):])
+                if t is not None:
+                    return t
+        raise KeyError(f"the model holds no tensor {name!r}")
+
+    def tensors(self) -> Dict[str, torch.Tensor]:
+        """Every loaded tensor by its full name (see :meth:`tensor`); absent optional ones
+        (a tied head) are left out."""
+        out: Dict[str, torch.Tensor] = {}
+        for prefix, part in self._places():
+            for ts in part.tensor_specs():
+                t = part.tensor(ts.name)
+                if t is not None:
+                    out[prefix + ts.name] = t
+        return out
+
     def is_ignored(self, name: str) -> bool:
         return any(fnmatch.fnmatchcase(name, pat) for pat in self.spec.ignore_tensors)
 

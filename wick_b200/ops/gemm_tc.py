@@ -99,6 +99,16 @@ def pack(w: torch.Tensor, gated: bool = False) -> torch.Tensor:
     return torch.cat(out, 0).contiguous() if len(out) > 1 else out[0].contiguous()
 
 
+def unpack(packed: torch.Tensor, rows: int, k: int, gated: bool = False) -> torch.Tensor:
+    """The [rows, k] matrix that :func:`pack` made ``packed`` from."""
+    tiles, k_blocks = packed.shape[:2]
+    full = packed.permute(0, 2, 1, 3).reshape(tiles * 128, k_blocks * 64)
+    if gated:
+        half = rows // 2
+        return torch.cat([full[:half, :k], full[(tiles // 2) * 128:(tiles // 2) * 128 + half, :k]], 0).contiguous()
+    return full[:rows, :k].contiguous()
+
+
 def gemm_tc_pair(a: torch.Tensor, b: torch.Tensor, b_rows: int, *, out: torch.Tensor, ldo: int, gated: bool = False,
                  pair_offset: int = 0, accumulate: bool = False, b_packed: bool = False, splits: int = 1,
                  split_stride: int = 0) -> None:
@@ -142,6 +152,10 @@ class Plan:
         # split keeps at least eight 64-wide steps of the inner dimension.
         self.decode_splits = max(1, min(2 * N_SMS // tiles, 8, k_blocks // 8))
         self.k_blocks = k_blocks
+
+    def matrix(self) -> torch.Tensor:
+        """The weight as it was given: [rows, k], row-major (a copy)."""
+        return unpack(self.w, self.rows, self.k, self.gated)
 
     def prompt_splits(self, t: int) -> int:
         """Runs of the inner dimension for ``t`` >= PAIR_MIN tokens: a few hundred tokens times

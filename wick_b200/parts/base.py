@@ -98,6 +98,13 @@ class Part:
         returns a tensor of the declared shape, or None for an absent optional
         one) and keep them on the device."""
 
+    def tensor(self, name: str) -> Optional[torch.Tensor]:
+        """The tensor held under the local ``name``, in the shape and layout a checkpoint
+        stores it in (on the device, in the dtype it is held in), however the part keeps
+        it for its kernels; None if the part holds none of that name.  For handing a
+        model's weights to another implementation."""
+        return None
+
     def weight_bytes(self) -> int:
         """Bytes of weights one forward pass of this part reads."""
         return 0

@@ -39,6 +39,12 @@ class Linear:
         if self.ctx.dtype == torch.bfloat16 and self._tensor_core() is not None:
             self.weight = None                 # the plan holds the matrix in its packed form
 
+    def rows(self, start: int, stop: int) -> torch.Tensor:
+        """Rows ``start..stop`` of the matrix as it was loaded, [stop - start, in] row-major,
+        whatever form it is held in."""
+        w = self.weight if self.weight is not None else self._tc.matrix()
+        return w[start:stop].contiguous()
+
     def weight_bytes(self) -> int:
         return self.out_features * self.in_features * (2 if self.ctx.dtype == torch.bfloat16 else 4)
 

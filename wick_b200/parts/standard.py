@@ -50,6 +50,9 @@ class RMSNorm(Norm):
     def load(self, fetch):
         self.weight = self.ctx.hold(fetch("weight"), "vector")
 
+    def tensor(self, name):
+        return self.weight if name == "weight" else None
+
     def forward(self, x, out_dtype, rows=None):
         return ops.rmsnorm(x, self.weight, self.eps, out_dtype, rows=rows)
 
@@ -146,6 +149,18 @@ class GQAttention(Mixer):
             self.q_norm.load(lambda n: fetch("q_norm." + n))
             self.k_norm.load(lambda n: fetch("k_norm." + n))
 
+    def tensor(self, name):
+        q, kv = self.q_dim, self.kv_dim
+        if name in ("q_proj.weight", "k_proj.weight", "v_proj.weight"):
+            lo, hi = {"q": (0, q), "k": (q, q + kv), "v": (q + kv, q + 2 * kv)}[name[0]]
+            return self.qkv.rows(lo, hi)
+        if name == "o_proj.weight":
+            return self.o.rows(0, self.width)
+        for prefix, norm in (("q_norm.", self.q_norm), ("k_norm.", self.k_norm)):
+            if name.startswith(prefix) and norm is not None:
+                return norm.tensor(name[len(prefix):])
+        return None
+
     def cache_need(self):
         return CacheNeed("paged_kv", kv_heads=self.kv_heads, head_dim=self.head_dim, window=self.window)
 
@@ -235,6 +250,14 @@ class GatedMLP(FeedForward):
         self.gate_up.load_rows([fetch("gate_proj.weight"), fetch("up_proj.weight")])
         self.down.load_rows([fetch("down_proj.weight")])
 
+    def tensor(self, name):
+        i = self.intermediate
+        if name == "gate_proj.weight":
+            return self.gate_up.rows(0, i)
+        if name == "up_proj.weight":
+            return self.gate_up.rows(i, 2 * i)
+        return self.down.rows(0, self.width) if name == "down_proj.weight" else None
+
     def weight_bytes(self):
         return self.gate_up.weight_bytes() + self.down.weight_bytes()
 
@@ -284,6 +307,9 @@ class TableEmbedding(Embedding):
     def load(self, fetch):
         self.weight = self.ctx.hold(fetch("weight"), "matrix")
 
+    def tensor(self, name):
+        return self.weight if name == "weight" else None
+
     def forward(self, tokens):
         return ops.embed(self.weight, tokens)
 
@@ -315,6 +341,9 @@ class LinearHead(Head):
         else:
             self.linear.load_rows([w])
             self.is_tied = False
+
+    def tensor(self, name):
+        return self.linear.rows(0, self.vocab) if name == "weight" and not self.is_tied else None
 
     def forward(self, x):
         return self.linear.forward(x, torch.float32)
