@@ -177,7 +177,7 @@ def decode_point(torch, wick, eng, pk, prompts, steps, warmup, repeats=REPEATS):
     """One decode workload as a dictionary: tokens a second (median region), spread, roofline."""
     regions, launches, kv_tokens, prompt_ms, finite = device_timed_decode(torch, wick, eng, prompts, steps, warmup, repeats)
     ms = statistics.median(regions)
-    step_bytes = eng.model.weight_bytes_per_step() + kv_tokens * eng.cache.bytes_per_token()
+    step_bytes = eng.model.weight_bytes_per_step() + eng.cache.read_bytes(int(kv_tokens), len(prompts))
     achieved = step_bytes / (ms * 1e-3) / 1e9
     return {"value": len(prompts) * 1e3 / ms, "ms_per_step": ms, "ms_min": min(regions), "ms_max": max(regions),
             "regions": len(regions), "gb_per_step": step_bytes / 1e9, "hbm_frac": achieved / pk["hbm_gbs"],

@@ -167,6 +167,42 @@ def test_groups_by_need_and_fixed_size_state():
 
 
 def test_windowed_storage_is_refused_clearly():
-    with pytest.raises(ValueError, match="windowed"):
+    with pytest.raises(ValueError, match="a window needs a storage kind of its own"):
         Cache([CacheNeed("paged_kv", kv_heads=1, head_dim=16, window=128)], max_tokens=64, dtype=torch.float32,
               device="cpu", allocate=False)
+    with pytest.raises(ValueError, match="unknown cache need ring"):
+        Cache([CacheNeed("ring", kv_heads=1, head_dim=16, window=128)], max_tokens=64, dtype=torch.float32,
+              device="cpu", allocate=False)
+
+
+def test_a_storage_kind_registered_from_outside_gets_its_group():
+    """Another kind of storage is an addition: a class registered under a new kind name
+    serves every need of that kind, beside the groups of the kinds that are built in."""
+    from wick_b200.cache import CacheView, Storage, register_storage
+
+    class LastPositions(Storage):
+        kind = "test_ring"
+
+        def shape(self):
+            n = self.need
+            return (self.n_entries, self.n_slots, 2, n.kv_heads, n.window, n.head_dim)
+
+        def view(self, idx, batch):
+            return CacheView(ring=self.tensor[idx], window=self.need.window)
+
+        def read_bytes(self, cached_tokens, n_seqs):
+            n = self.need
+            return n_seqs * self.n_entries * 2 * n.kv_heads * n.window * n.head_dim * self.element_size()
+
+    register_storage("test_ring", LastPositions)
+    needs = [CacheNeed("paged_kv", kv_heads=2, head_dim=16), CacheNeed("test_ring", kv_heads=1, head_dim=8, window=4),
+             CacheNeed("test_ring", kv_heads=1, head_dim=8, window=4), CacheNeed("state", shape=(5,), dtype=torch.float32)]
+    c = Cache(needs, max_tokens=128, dtype=torch.float32, device="cpu", max_seqs=3)
+    assert [g.need.kind for g in c.groups] == ["paged_kv", "test_ring", "state"]
+    assert c.groups[1].storage.shape == (2, 4, 2, 1, 4, 8)
+    v = c.view(2)
+    assert v.window == 4 and v.ring.shape == (4, 2, 1, 4, 8) and v.kv is None
+    # a decode step of 3 sequences holding 100 positions: the paged group reads by position,
+    # the ring by its window, the records by sequence
+    assert c.read_bytes(100, 3) == 100 * 2 * 2 * 16 * 4 + 3 * 2 * 2 * 1 * 4 * 8 * 4 + 3 * 5 * 4
+    assert c.bytes_per_token() == 2 * 2 * 16 * 4

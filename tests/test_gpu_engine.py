@@ -252,9 +252,10 @@ def test_wanted_rows_come_in_order_of_entries_and_want():
     eng = make_engine(name, dtype)
     a, b = random_tokens(512, 9, 50), random_tokens(512, 4, 51)
     sa, sb = eng.open_seq(), eng.open_seq()
-    got = eng.step([sa, sb], [a, b], [[8, 0], [2]])
+    got = eng.step([sa, sb], [a, b], [[8, 0, 8], [2, 2]])       # a place may be asked for more than once
     ra, rb = plain_logits(name, a), plain_logits(name, b)
-    assert_logits_close(got, torch.stack([ra[8], ra[0], rb[2]]), dtype, "want order")
+    assert_logits_close(got, torch.stack([ra[8], ra[0], ra[8], rb[2], rb[2]]), dtype, "want order")
+    assert torch.equal(got[0], got[2]) and torch.equal(got[3], got[4])
     eng.close_seq(sa)
     eng.close_seq(sb)
 

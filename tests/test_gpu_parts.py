@@ -82,7 +82,7 @@ def test_attention_part(dtype, qk_norm):
     T = 90
     x = torch.randn(T, width).to(dtype)
     b = FakeBatch([T], [0], [[2, 1]]).sb
-    b.workspace, b.kv_bound = Workspace(torch.device("cuda")), T
+    b.workspace = Workspace(torch.device("cuda"))
     out = att.forward(x.cuda(), b, cache.view(0), True)
     # plain: the same weights under the names the plain block expects
     w = {"L.self_attn." + k: v.float() for k, v in t.items()}
@@ -105,7 +105,7 @@ def test_attention_part(dtype, qk_norm):
     # one more token through the decode form
     x1 = torch.randn(1, width).to(dtype)
     b1 = FakeBatch([1], [T], [[2, 1]]).sb
-    b1.workspace, b1.kv_bound = b.workspace, T + 1
+    b1.workspace = b.workspace
     out1 = att.forward(x1.cuda(), b1, cache.view(0), True)
     if qk_norm:
         ref1, _ = P.attention_block(torch.cat([x, x1]).float(), w, "L.", cfg, torch.arange(T + 1))
@@ -138,7 +138,9 @@ def test_embedding_and_head_parts(dtype):
     for tied in (True, False):
         head = build_part("head", wick.PartSpec("linear", {"vocab": 333, "width": 72, "tied": tied}), ctx(dtype))
         own = (torch.randn(333, 72) / 4).to(torch.bfloat16)
-        head.load(lambda n: own, emb)
+        assert head.PEERS == ("embedding",)
+        head.attach({"embedding": emb})
+        head.load(lambda n: own)
         logits = head.forward(x.cuda())
         assert logits.dtype == torch.float32 and head.is_tied == tied
         ref = x.float() @ (table if tied else own).float().T

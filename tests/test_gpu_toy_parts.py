@@ -320,3 +320,144 @@ def test_a_routed_feed_forward_and_another_position_encoding(graphs):
             assert_logits_close(got[i], r[len(s) - k], "float32", "routed decode")
     for sl in slots:
         eng.close_seq(sl)
+
+
+# ---------------------------------------------------------------------------
+# A mixer that reads only the last few positions, with a kind of cache storage of its own:
+# both are registered here; the package's files know nothing of either.
+from wick_b200.cache import CacheView, Storage, register_storage  # noqa: E402
+
+
+class LastRows(Storage):
+    """[entries, slots, window, width] float32: row ``position % window`` of a sequence's
+    slot holds what the mixer stored for that position."""
+    kind = "toy_last_rows"
+
+    def shape(self):
+        return (self.n_entries, self.n_slots, self.need.window) + tuple(self.need.shape)
+
+    def view(self, idx, batch):
+        return CacheView(rows=self.tensor[idx], slots=batch.slots, window=self.need.window)
+
+    def open_seq(self, slot):
+        self.tensor[:, slot] = float("nan")                   # nothing stored yet: a read of it must show
+
+    def read_bytes(self, cached_tokens, n_seqs):
+        n = self.element_size() * self.need.window
+        for d in self.need.shape:
+            n *= d
+        return n_seqs * self.n_entries * n
+
+
+register_storage("toy_last_rows", LastRows)
+
+
+class WindowMean(Mixer):
+    """out_t = W mean(x_s for s in the last ``window`` positions up to t)."""
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.width, self.window = int(params["width"]), int(params["window"])
+
+    def tensor_specs(self):
+        return [TensorSpec("mix.weight", (self.width, self.width))]
+
+    def load(self, fetch):
+        self.w = self.ctx.hold(fetch("mix.weight"), "matrix")
+
+    def cache_need(self):
+        return CacheNeed("toy_last_rows", window=self.window, shape=(self.width,), dtype=torch.float32)
+
+    def forward(self, x, batch, cache, write_cache):
+        W = self.window
+        xf = x.float()
+        slots = cache.slots.long()
+        if batch.is_decode:                                   # device tensors only: safe inside a captured step
+            pos = batch.positions.long()
+            cache.rows[slots, pos % W] = xf
+            have = torch.clamp(pos + 1, max=W)                # positions stored so far, at most the window
+            keep = (torch.arange(W, device=x.device)[None, :] < have[:, None])
+            # rows of the ring that hold one of the last `have` positions: all of them once the
+            # ring is full, rows 0..pos before
+            rows = torch.where(keep[:, :, None], cache.rows[slots], torch.zeros((), device=x.device))
+            means = rows.sum(1) / have[:, None].float()
+        else:
+            out, t0 = [], 0
+            for b, n in enumerate(batch.q_lens):
+                start = batch.starts[b]
+                for t in range(n):
+                    p = start + t
+                    cache.rows[slots[b], p % W] = xf[t0 + t]
+                    have = min(p + 1, W)
+                    idx = torch.tensor([(p - i) % W for i in range(have)], device=x.device)
+                    out.append(cache.rows[slots[b]][idx].sum(0) / have)
+                t0 += n
+            means = torch.stack(out)
+        return (means.to(self.ctx.dtype).float() @ self.w.float().T).unsqueeze(0)
+
+
+register_part("mixer", "toy_window_mean", WindowMean)
+
+
+def build_window_spec(cfg):
+    spec = wick.get_architecture("qwen3").build_spec(cfg)
+    layers = list(spec.layers)
+    layers[1] = dataclasses.replace(layers[1], mixer=wick.PartSpec("toy_window_mean", {"width": cfg.hidden_size, "window": 5}),
+                                    names={**layers[1].names, "mixer": "win."})
+    return dataclasses.replace(spec, layers=tuple(layers))
+
+
+wick.register_architecture(wick.Architecture(("ToyWindowForCausalLM",), wick.Qwen3Config, build_window_spec))
+
+
+def plain_window_forward(cfg, w, tokens, window):
+    toks = torch.as_tensor(tokens)
+    T = len(tokens)
+    x = w["model.embed_tokens.weight"][toks]
+    for layer in range(cfg["layers"]):
+        p = f"model.layers.{layer}."
+        xn = P.rms_norm(x, w[p + "input_layernorm.weight"], cfg["eps"])
+        if layer == 1:
+            d = torch.stack([xn[max(0, t - window + 1):t + 1].mean(0) for t in range(T)]) @ w[p + "win.mix.weight"].T
+        else:
+            d, _ = P.attention_block(xn, w, p, cfg, torch.arange(T))
+        x = x + d
+        xn = P.rms_norm(x, w[p + "post_attention_layernorm.weight"], cfg["eps"])
+        x = x + P.swiglu(xn, w, p)
+    xn = P.rms_norm(x, w["model.norm.weight"], cfg["eps"])
+    head = w["model.embed_tokens.weight"] if cfg["tied"] else w["lm_head.weight"]
+    return xn @ head.T
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_a_windowed_mixer_with_a_storage_kind_of_its_own(graphs):
+    """One layer keeps the last five positions in a ring per sequence (a storage class registered
+    in this file), the others all keys in pages: groups of layers with different needs, each with
+    storage of its own.  Prompts shorter and longer than the window, decoding across the ring's
+    wrap, slots used again (a new sequence must not see the last one's rows)."""
+    cfg = wick.config_from_json(dict(CONFIG_B, architectures=["ToyWindowForCausalLM"]))
+    d = os.path.join(tmp_root(), "toy-window")
+    wick.write_random_model(cfg, 8, d, dtype=torch.float32)
+    eng = wick.Engine.from_dir(d, dtype="float32", max_tokens=512, use_graphs=graphs)
+    assert [g.need.kind for g in eng.cache.groups] == ["paged_kv", "toy_last_rows"]
+    assert [len(g.entries) for g in eng.cache.groups] == [2, 1]
+    assert eng.cache.groups[1].storage.shape[2:] == (5, 96)
+    # what a decode step reads: pages by position, the ring by sequence
+    assert eng.cache.read_bytes(100, 2) == 100 * eng.cache.bytes_per_token() + 2 * 5 * 96 * 4
+    pc, pw = P.read_model_dir(d)
+    seqs = [random_tokens(1000, n, 600 + n) for n in (3, 12, 7)]
+    refs = [plain_window_forward(pc, pw, s + random_tokens(1000, 9, 700 + len(s)), 5) for s in seqs]
+    full = [s + random_tokens(1000, 9, 700 + len(s)) for s in seqs]
+    for rnd in range(2):
+        slots = [eng.open_seq() for _ in seqs]
+        got = eng.step(slots, seqs, [list(range(len(s))) for s in seqs]).clone()
+        off = 0
+        for s, r in zip(seqs, refs):
+            assert_logits_close(got[off:off + len(s)], r[:len(s)], "float32", f"window prompt round {rnd}")
+            off += len(s)
+        for k in range(9):
+            got = eng.step(slots, [[f[len(s) + k]] for s, f in zip(seqs, full)]).clone()
+            for i, (s, r) in enumerate(zip(seqs, refs)):
+                assert_logits_close(got[i], r[len(s) + k], "float32", f"window decode {k} round {rnd}")
+        for sl in slots:
+            eng.close_seq(sl)

@@ -9,10 +9,13 @@
   ``ceil(length / 64)`` pages, so the pool's size is the number of tokens (each
   sequence rounded up to 64) that live sequences may hold at once.
 * Schedule entries (layers as they run) with equal needs form a **group** with
-  one storage tensor of its own: ``paged_kv`` groups [entries, pages, 2,
-  kv_heads, 64, head_dim]; ``state`` groups [entries, slots, *shape], a record
-  of fixed size per sequence that is zeroed when the sequence opens.  All paged
-  groups share the page ids (page p of a sequence is page p in each group).
+  storage of its own, of the class registered for the need's kind
+  (:func:`register_storage`): ``paged_kv`` groups [entries, pages, 2, kv_heads,
+  64, head_dim]; ``state`` groups [entries, slots, *shape], a record of fixed
+  size per sequence that is zeroed when the sequence opens.  All paged groups
+  share the page ids (page p of a sequence is page p in each group).  Another
+  kind of storage (a ring of the last positions, say) is another registered
+  class; nothing here changes for it.
 * Page 0 and slot 0 are never handed out: padded batch entries point there.
 
 The bookkeeping is host-side Python over :class:`IndexPool` and needs no GPU;
@@ -25,10 +28,9 @@ from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
+from ..layout import PAGE
 from ..parts.base import CacheNeed
 from .pool import IndexPool, PoolError, PoolExhausted
-
-PAGE = 64
 
 
 class CacheFull(PoolExhausted):
@@ -44,12 +46,109 @@ class SeqRecord:
 
 
 class CacheView:
-    """What one schedule entry's mixer sees of the cache during a step."""
+    """What one schedule entry's mixer sees of the cache during a step: ``kv`` (this entry's
+    keys and values), ``state`` with ``slots`` (this entry's records and the step's slot of
+    each sequence), or whatever else a storage class of another kind hands out by keyword."""
 
-    __slots__ = ("kv", "state", "slots")
-
-    def __init__(self, kv=None, state=None, slots=None):
+    def __init__(self, kv=None, state=None, slots=None, **more):
         self.kv, self.state, self.slots = kv, state, slots
+        for k, v in more.items():
+            setattr(self, k, v)
+
+
+class Storage:
+    """The storage of one group of schedule entries with equal needs.
+
+    A subclass is registered under the ``kind`` of the :class:`CacheNeed` it serves.  It
+    is made with the need, the number of entries in the group, the cache's sizes (pages
+    including the padding page 0, slots including the padding slot 0), the element type
+    and the device; it allocates in :meth:`allocate`, hands one entry's part of itself to
+    a mixer in :meth:`view`, prepares a slot for a new sequence in :meth:`open_seq`, and
+    says how many bytes a step reads from it in :meth:`read_bytes`."""
+
+    kind = ""
+
+    def __init__(self, need: CacheNeed, n_entries: int, *, n_pages: int, n_slots: int, dtype: torch.dtype,
+                 device: torch.device):
+        self.need, self.n_entries, self.n_pages, self.n_slots = need, n_entries, n_pages, n_slots
+        self.dtype, self.device = dtype, device
+        self.tensor: Optional[torch.Tensor] = None
+
+    def shape(self) -> Tuple[int, ...]:
+        raise NotImplementedError
+
+    def allocate(self) -> None:
+        self.tensor = torch.zeros(self.shape(), dtype=self.dtype, device=self.device)
+
+    def view(self, idx: int, batch) -> "CacheView":
+        raise NotImplementedError
+
+    def open_seq(self, slot: int) -> None:
+        """A sequence starts in ``slot``."""
+
+    def read_bytes(self, cached_tokens: int, n_seqs: int) -> int:
+        """Bytes a decode step reads from this group for ``n_seqs`` sequences that hold
+        ``cached_tokens`` positions between them."""
+        return 0
+
+    def element_size(self) -> int:
+        return torch.empty((), dtype=self.dtype).element_size()
+
+
+class PagedKV(Storage):
+    """Keys and values of every position: [entries, pages, 2, kv_heads, 64, head_dim]."""
+    kind = "paged_kv"
+
+    def __init__(self, need, n_entries, **kw):
+        super().__init__(need, n_entries, **kw)
+        if need.window is not None:
+            raise ValueError("paged key/value storage keeps every position; a window needs a storage kind of its own")
+
+    def shape(self):
+        n = self.need
+        return (self.n_entries, self.n_pages, 2, n.kv_heads, PAGE, n.head_dim)
+
+    def view(self, idx, batch):
+        return CacheView(kv=self.tensor[idx])
+
+    def bytes_per_token(self) -> int:
+        return self.n_entries * 2 * self.need.kv_heads * self.need.head_dim * self.element_size()
+
+    def read_bytes(self, cached_tokens, n_seqs):
+        return cached_tokens * self.bytes_per_token()
+
+
+class StateRecords(Storage):
+    """A record of fixed shape per sequence: [entries, slots, *shape], zero when a sequence starts."""
+    kind = "state"
+
+    def shape(self):
+        return (self.n_entries, self.n_slots) + tuple(self.need.shape)
+
+    def view(self, idx, batch):
+        return CacheView(state=self.tensor[idx], slots=None if batch is None else batch.slots)
+
+    def open_seq(self, slot):
+        if self.tensor is not None:
+            self.tensor[:, slot].zero_()
+
+    def read_bytes(self, cached_tokens, n_seqs):
+        n = self.element_size()
+        for d in self.need.shape:
+            n *= d
+        return n_seqs * self.n_entries * n
+
+
+_STORAGE: Dict[str, type] = {}
+
+
+def register_storage(kind: str, cls: type) -> type:
+    _STORAGE[kind] = cls
+    return cls
+
+
+register_storage("paged_kv", PagedKV)
+register_storage("state", StateRecords)
 
 
 class _Group:
@@ -57,7 +156,11 @@ class _Group:
         self.need = need
         self.dtype = need.dtype or dtype
         self.entries: List[int] = []
-        self.storage: Optional[torch.Tensor] = None
+        self.store: Optional[Storage] = None
+
+    @property
+    def storage(self) -> Optional[torch.Tensor]:
+        return None if self.store is None else self.store.tensor
 
     def key(self):
         n = self.need
@@ -85,32 +188,29 @@ class Cache:
         for i, need in enumerate(needs):
             if need is None:
                 continue
-            if need.kind not in ("paged_kv", "state"):
-                raise ValueError(f"unknown cache need {need.kind}")
-            if need.kind == "paged_kv" and need.window is not None:
-                raise ValueError("windowed key/value storage is not built")
+            if need.kind not in _STORAGE:
+                raise ValueError(f"unknown cache need {need.kind} (registered: {', '.join(sorted(_STORAGE))})")
             g = _Group(need, dtype)
             g = by_key.setdefault(g.key(), g)
             if not g.entries:
                 self.groups.append(g)
             self.entry_place[i] = (g, len(g.entries))
             g.entries.append(i)
-        if allocate:
-            for g in self.groups:
-                n = g.need
-                if n.kind == "paged_kv":
-                    shape = (len(g.entries), self.n_pages, 2, n.kv_heads, PAGE, n.head_dim)
-                else:
-                    shape = (len(g.entries), self.max_seqs + 1) + tuple(n.shape)
-                g.storage = torch.zeros(shape, dtype=g.dtype, device=self.device)
+        for g in self.groups:
+            g.store = _STORAGE[g.need.kind](g.need, len(g.entries), n_pages=self.n_pages, n_slots=self.max_seqs + 1,
+                                            dtype=g.dtype, device=self.device)
+            if allocate:
+                g.store.allocate()
 
     # ---- sizes -------------------------------------------------------------
     def bytes_per_token(self) -> int:
-        n = 0
-        for g in self.groups:
-            if g.need.kind == "paged_kv":
-                n += len(g.entries) * 2 * g.need.kv_heads * g.need.head_dim * torch.empty((), dtype=g.dtype).element_size()
-        return n
+        """Bytes of keys and values that one cached position takes in all paged groups."""
+        return sum(g.store.bytes_per_token() for g in self.groups if isinstance(g.store, PagedKV))
+
+    def read_bytes(self, cached_tokens: int, n_seqs: int) -> int:
+        """Bytes one decode step reads from the cache: every group's share for ``n_seqs``
+        sequences that hold ``cached_tokens`` positions between them."""
+        return sum(g.store.read_bytes(cached_tokens, n_seqs) for g in self.groups)
 
     def storage_bytes(self) -> int:
         return sum(g.storage.numel() * g.storage.element_size() for g in self.groups if g.storage is not None)
@@ -124,8 +224,7 @@ class Cache:
         slot = self.slots.alloc()
         self.seqs[slot] = SeqRecord()
         for g in self.groups:
-            if g.need.kind == "state" and g.storage is not None:
-                g.storage[:, slot].zero_()
+            g.store.open_seq(slot)
         return slot
 
     def _rec(self, slot: int) -> SeqRecord:
@@ -203,6 +302,4 @@ class Cache:
         if place is None:
             return None
         g, idx = place
-        if g.need.kind == "paged_kv":
-            return CacheView(kv=g.storage[idx])
-        return CacheView(state=g.storage[idx], slots=None if batch is None else batch.slots)
+        return g.store.view(idx, batch)

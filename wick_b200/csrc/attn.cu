@@ -23,7 +23,6 @@ namespace wick {
 
 constexpr int HD = WICK_HD;
 static_assert(HD % 16 == 0 && HD >= 16 && HD <= 256, "head_dim must be a multiple of 16 in [16, 256]");
-constexpr int kPage = 64;
 
 // ============================================================================
 // Prompt form.  One block (128 threads) per (64-query tile, head).  Thread
@@ -56,16 +55,17 @@ __device__ __forceinline__ void load_page_tile(const T* __restrict__ src, float*
 template <typename T>
 __global__ void __launch_bounds__(128)
 attn_prompt_kernel(const T* __restrict__ q, const T* __restrict__ kv, T* __restrict__ out,
-                   const int* __restrict__ tile_seq, const int* __restrict__ tile_q0,
-                   const int* __restrict__ cu_seqlens, const int* __restrict__ start,
+                   const int* __restrict__ cu_seqlens, int n_seqs, const int* __restrict__ start,
                    const int* __restrict__ page_table, int table_width, int n_heads, int n_kv, float scale) {
     extern __shared__ float smem[];
     float* Qs = smem;                       // [QT][QS]
     float* Ks = Qs + QT * QS;               // [64][HD]
     float* Vs = Ks + kPage * HD;            // [64][HD]
 
-    const int tile = blockIdx.x, head = blockIdx.y;
-    const int b = tile_seq[tile], q0 = tile_q0[tile];
+    const int head = blockIdx.y;
+    int b, q0;
+    find_work_item(cu_seqlens, n_seqs, QT, blockIdx.x, b, q0);
+    if (b < 0) return;
     const int tok0 = cu_seqlens[b], q_len = cu_seqlens[b + 1] - tok0;
     const int s0 = start[b];
     const int rows = min(QT, q_len - q0);
@@ -352,8 +352,7 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ part_o, const
 }
 
 template <typename T>
-int attn_prompt(const void* q, const void* kv, void* out, const int* tile_seq, const int* tile_q0, int n_tiles,
-                const int* cu_seqlens, const int* start, const int* page_table, int table_width, int n_heads,
+int attn_prompt(const void* q, const void* kv, void* out, int n_tiles, const int* cu_seqlens, int n_seqs, const int* start, const int* page_table, int table_width, int n_heads,
                 int n_kv, float scale, cudaStream_t s) {
     WICK_REQUIRE(n_heads > 0 && n_kv > 0 && n_heads % n_kv == 0, "attention: %d heads over %d kv heads", n_heads, n_kv);
     WICK_REQUIRE(n_heads <= 65535, "attention: %d heads is beyond the grid limit", n_heads);
@@ -364,8 +363,8 @@ int attn_prompt(const void* q, const void* kv, void* out, const int* tile_seq, c
         WICK_CUDA(cudaFuncSetAttribute(attn_prompt_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         raised = true;
     }
-    attn_prompt_kernel<T><<<dim3(n_tiles, n_heads), 128, smem, s>>>((const T*)q, (const T*)kv, (T*)out, tile_seq,
-                                                                  tile_q0, cu_seqlens, start, page_table,
+    attn_prompt_kernel<T><<<dim3(n_tiles, n_heads), 128, smem, s>>>((const T*)q, (const T*)kv, (T*)out, cu_seqlens,
+                                                                  n_seqs, start, page_table,
                                                                   table_width, n_heads, n_kv, scale);
     return check_launch("attn_prompt");
 }
@@ -400,16 +399,16 @@ WICK_API int wick_attn_head_dim() { return HD; }
 WICK_API int wick_attn_decode_plain_split() { return SPLIT; }
 
 // q, out: [n_tokens, n_heads, HD]; kv: one schedule entry's cache.
-WICK_API int wick_attn_prompt_bf16(const void* q, const void* kv, void* out, const int* tile_seq, const int* tile_q0,
-                                   int n_tiles, const int* cu_seqlens, const int* start, const int* page_table,
+WICK_API int wick_attn_prompt_bf16(const void* q, const void* kv, void* out, int n_tiles, const int* cu_seqlens,
+                                   int n_seqs, const int* start, const int* page_table,
                                    int table_width, int n_heads, int n_kv, float scale, void* s) {
-    return attn_prompt<bf16>(q, kv, out, tile_seq, tile_q0, n_tiles, cu_seqlens, start, page_table, table_width,
+    return attn_prompt<bf16>(q, kv, out, n_tiles, cu_seqlens, n_seqs, start, page_table, table_width,
                              n_heads, n_kv, scale, (cudaStream_t)s);
 }
-WICK_API int wick_attn_prompt_f32(const void* q, const void* kv, void* out, const int* tile_seq, const int* tile_q0,
-                                  int n_tiles, const int* cu_seqlens, const int* start, const int* page_table,
+WICK_API int wick_attn_prompt_f32(const void* q, const void* kv, void* out, int n_tiles, const int* cu_seqlens,
+                                  int n_seqs, const int* start, const int* page_table,
                                   int table_width, int n_heads, int n_kv, float scale, void* s) {
-    return attn_prompt<float>(q, kv, out, tile_seq, tile_q0, n_tiles, cu_seqlens, start, page_table, table_width,
+    return attn_prompt<float>(q, kv, out, n_tiles, cu_seqlens, n_seqs, start, page_table, table_width,
                               n_heads, n_kv, scale, (cudaStream_t)s);
 }
 // scratch: float32 [scratch_floats], at least n_seqs*n_heads*ceil(max_kv_len/256)*(HD+2).

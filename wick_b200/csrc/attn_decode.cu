@@ -24,7 +24,6 @@ namespace wick {
 namespace fastdecode {
 
 constexpr int HD = WICK_HD;
-constexpr int kPage = 64;
 constexpr int GT = 4;                                  // query heads handled per pass
 
 template <typename T> struct Shape {

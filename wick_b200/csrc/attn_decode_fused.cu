@@ -38,7 +38,6 @@ namespace decodefused {
 
 constexpr bool SUPPORTED = WICK_HD == 64 || WICK_HD == 128;
 constexpr int HD = SUPPORTED ? WICK_HD : 64;           // other head sizes: the entry point refuses, the kernel is never launched
-constexpr int kPage = 64;
 constexpr int PAGES = 2;
 constexpr int CHUNK = PAGES * kPage;
 constexpr int NH = 8;                                  // query heads of a kv head (the 8-wide side of the instruction)

@@ -31,7 +31,6 @@ namespace decodemma {
 
 constexpr int HD = WICK_HD;
 constexpr bool SUPPORTED = HD % 64 == 0 && HD <= 128;
-constexpr int kPage = 64;
 constexpr int PAGES = 2;
 constexpr int SPLIT = PAGES * kPage;
 constexpr int NH = 8;                                  // query heads per item (the 8-wide side of the instruction)

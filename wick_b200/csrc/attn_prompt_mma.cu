@@ -20,7 +20,6 @@ namespace wick {
 namespace promptmma {
 
 constexpr int HD = WICK_HD;
-constexpr int kPage = 64;
 constexpr int QT = 64;
 constexpr int CHUNKS = HD / 8;                       // 16-byte chunks per row
 constexpr bool SWZ = CHUNKS % 8 == 0;
@@ -69,8 +68,7 @@ __device__ __forceinline__ void load_tile(bf16* dst, const bf16* src, int valid_
 
 __global__ void __launch_bounds__(128)
 attn_prompt_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv, bf16* __restrict__ out,
-                       const int* __restrict__ tile_seq, const int* __restrict__ tile_q0,
-                       const int* __restrict__ cu_seqlens, const int* __restrict__ start,
+                       const int* __restrict__ cu_seqlens, int n_seqs, const int* __restrict__ start,
                        const int* __restrict__ page_table, int table_width, int n_tiles, int n_heads, int n_kv,
                        float scale) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
@@ -82,9 +80,10 @@ attn_prompt_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv, 
     q = fresh(q);
     kv = fresh(kv);
 
-    const int tile = n_tiles - 1 - blockIdx.x;                 // long tiles (late rows of long prompts) first
     const int head = blockIdx.y;
-    const int b = tile_seq[tile], q0 = tile_q0[tile];
+    int b, q0;
+    find_work_item(cu_seqlens, n_seqs, QT, n_tiles - 1 - (int)blockIdx.x, b, q0);   // long tiles (late rows of long prompts) first
+    if (b < 0) return;
     const int tok0 = cu_seqlens[b], q_len = cu_seqlens[b + 1] - tok0;
     const int s0 = start[b];
     const int rows = min(QT, q_len - q0);
@@ -253,8 +252,8 @@ using namespace wick;
 WICK_API int wick_attn_prompt_mma_supported() { return promptmma::SUPPORTED ? 1 : 0; }
 
 // Same arguments as wick_attn_prompt_bf16 (attn.cu).
-WICK_API int wick_attn_prompt_mma_bf16(const void* q, const void* kv, void* out, const int* tile_seq, const int* tile_q0,
-                                       int n_tiles, const int* cu_seqlens, const int* start, const int* page_table,
+WICK_API int wick_attn_prompt_mma_bf16(const void* q, const void* kv, void* out, int n_tiles, const int* cu_seqlens,
+                                       int n_seqs, const int* start, const int* page_table,
                                        int table_width, int n_heads, int n_kv, float scale, void* s) {
     using namespace promptmma;
     WICK_REQUIRE(SUPPORTED, "attention (tensor cores): head_dim %d is beyond 128", HD);
@@ -268,7 +267,7 @@ WICK_API int wick_attn_prompt_mma_bf16(const void* q, const void* kv, void* out,
         raised = true;
     }
     WICK_CUDA(launch(attn_prompt_mma_kernel, dim3(n_tiles, n_heads), dim3(128), smem, (cudaStream_t)s, (const bf16*)q,
-                     (const bf16*)kv, (bf16*)out, tile_seq, tile_q0, cu_seqlens, start, page_table, table_width, n_tiles,
+                     (const bf16*)kv, (bf16*)out, cu_seqlens, n_seqs, start, page_table, table_width, n_tiles,
                      n_heads, n_kv, scale));
     return check_launch("attn_prompt_mma");
 }

@@ -44,7 +44,6 @@ namespace prompttc {
 
 constexpr bool SUPPORTED = WICK_HD == 64 || WICK_HD == 128;
 constexpr int HD = SUPPORTED ? WICK_HD : 64;           // other head sizes: the entry point refuses, the kernel is never launched
-constexpr int kPage = 64;
 constexpr int BQ = 128;                                // query rows of a block
 constexpr int BK = 128;                                // keys of an inner step (two pages)
 constexpr int PANELS = HD / 64;                        // 64-column panels of a head row
@@ -145,8 +144,8 @@ __device__ __forceinline__ float ex2(float x) {
 
 __global__ void __launch_bounds__(THREADS, 1)
 attn_prompt_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map,
-                      bf16* __restrict__ out, const int* __restrict__ tile_seq, const int* __restrict__ tile_q0,
-                      const int* __restrict__ cu_seqlens, const int* __restrict__ start_arr,
+                      bf16* __restrict__ out, const int* __restrict__ cu_seqlens, int n_seqs,
+                      const int* __restrict__ start_arr,
                       const int* __restrict__ page_table, int table_width, int n_tiles, int n_heads, int n_kv,
                       float scale, int* status) {
     extern __shared__ uint8_t smem_raw[];
@@ -158,10 +157,10 @@ attn_prompt_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_co
 
     pdl_trigger();
     // longest first: the last work items of a sequence see the most keys
-    const int tile = n_tiles - 1 - (int)blockIdx.x;
-    const int q0 = tile_q0[tile];                                  // written by the host before the step: no kernel produces it
-    if (q0 % BQ != 0) return;                                      // the odd 64-row item belongs to its even neighbour's block
-    const int b = tile_seq[tile];
+    // (the step's description is written by the host before the step: no kernel produces it)
+    int b, q0;
+    find_work_item(cu_seqlens, n_seqs, 64, n_tiles - 1 - (int)blockIdx.x, b, q0);
+    if (b < 0 || q0 % BQ != 0) return;                             // the odd 64-row item belongs to its even neighbour's block
     const int head = blockIdx.y, kvh = head / (n_heads / n_kv);
     const int tok0 = cu_seqlens[b], q_len = cu_seqlens[b + 1] - tok0, start = start_arr[b];
     const int kv_len = start + q_len;
@@ -435,10 +434,10 @@ WICK_API int wick_attn_prompt_tc_supported() { return prompttc::SUPPORTED ? 1 : 
 
 // q, out: bfloat16 [n_tokens, n_heads, HD]; kv: one schedule entry's cache, bfloat16
 // [kv_pages, 2, n_kv, 64, HD] (it already holds the new tokens' keys and values);
-// tile_seq / tile_q0: the step's 64-row work items in sequence order; status: device
-// int (code 7 if a block gave up waiting).
+// n_tiles: the step's 64-row work items (one per 64 new tokens of a sequence, numbered
+// sequence by sequence); status: device int (code 7 if a block gave up waiting).
 WICK_API int wick_attn_prompt_tc_bf16(const void* q, long long n_tokens, const void* kv, long long kv_pages, void* out,
-                                      const int* tile_seq, const int* tile_q0, int n_tiles, const int* cu_seqlens,
+                                      int n_tiles, const int* cu_seqlens, int n_seqs,
                                       const int* start, const int* page_table, int table_width, int n_heads, int n_kv,
                                       float scale, int* status, void* s) {
     using namespace prompttc;
@@ -455,7 +454,7 @@ WICK_API int wick_attn_prompt_tc_bf16(const void* q, long long n_tokens, const v
         raised = true;
     }
     WICK_CUDA(launch(attn_prompt_tc_kernel, dim3(n_tiles, n_heads), dim3(THREADS), (size_t)SMEM_BYTES, (cudaStream_t)s, q_map,
-                     kv_map, (bf16*)out, tile_seq, tile_q0, cu_seqlens, start, page_table, table_width, n_tiles, n_heads,
+                     kv_map, (bf16*)out, cu_seqlens, n_seqs, start, page_table, table_width, n_tiles, n_heads,
                      n_kv, scale, status));
     return check_launch("attn_prompt_tc");
 }

@@ -129,6 +129,41 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 
 inline int ceil_div(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }
 
+// Positions per cache page.  The Python side carries the same number (wick_b200/layout.py);
+// every library exports it (wick_page_size) and the loader refuses a library that differs.
+constexpr int kPage = 64;
+
+// The work items of a step whose new tokens are cut into runs of `rows` per sequence are
+// numbered sequence by sequence; this finds the sequence b and the first row q0 of item
+// `item` from the step's cu_seqlens (which the host writes: no kernel produces it, so it may
+// be read before griddepcontrol.wait).  All 32 lanes of the calling warp take part; every
+// lane gets the result; b is -1 beyond the last item.
+__device__ __forceinline__ void find_work_item(const int* __restrict__ cu_seqlens, int n_seqs, int rows, int item, int& b, int& q0) {
+    const int lane = threadIdx.x & 31;
+    int before = 0;
+    for (int s0 = 0; s0 < n_seqs; s0 += 32) {
+        const int s = s0 + lane;
+        const int mine = s < n_seqs ? (cu_seqlens[s + 1] - cu_seqlens[s] + rows - 1) / rows : 0;
+        int upto = mine;                                         // items of sequences s0 .. s
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int t = __shfl_up_sync(0xffffffffu, upto, o);
+            if (lane >= o) upto += t;
+        }
+        const int total = __shfl_sync(0xffffffffu, upto, 31);
+        if (item < before + total) {
+            const unsigned holds = __ballot_sync(0xffffffffu, item - before < upto);
+            const int l = __ffs(holds) - 1;
+            b = s0 + l;
+            q0 = (item - before - __shfl_sync(0xffffffffu, upto - mine, l)) * rows;
+            return;
+        }
+        before += total;
+    }
+    b = -1;
+    q0 = 0;
+}
+
 // ---- programmatic dependent launch -------------------------------------------
 // Kernels are launched so that the next kernel in the stream may be scheduled
 // while this one still runs.  A kernel therefore (1) lets its successor start
@@ -177,6 +212,9 @@ inline cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
 }
 
 }  // namespace wick
+
+// The page size this library was built with.
+extern "C" __attribute__((visibility("default"), weak)) int wick_page_size() { return wick::kPage; }
 
 // The message of the last failed call of this library on this thread.
 extern "C" __attribute__((visibility("default"), weak)) const char* wick_last_error() { return wick::error_buffer(); }

@@ -12,7 +12,6 @@
 
 namespace wick {
 
-constexpr int kPage = 64;
 
 // ---- embedding -------------------------------------------------------------
 template <typename T>
@@ -47,8 +46,9 @@ __device__ __forceinline__ void st4(__nv_bfloat16* p, float a, float b, float c,
 __device__ __forceinline__ float rms_scale(float ss, int width, float eps) { return 1.0f / sqrtf(__fadd_rn(__fdiv_rn(ss, (float)width), eps)); }
 
 // One block per output row i.  Source row r = rows ? rows[i] : i.  If delta is
-// given, x[r] += delta[0][r] + delta[1][r] + ... (index order) and is written
-// back before it is normalised.
+// given, x[r] + delta[0][r] + delta[1][r] + ... (index order) is normalised; without
+// `rows` the sum is also written back to x.  With `rows` x stays as it is: a row may be
+// named twice, and two blocks that both wrote it back could each read the other's sum.
 template <typename TOut>
 __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int splits,
                                int64_t split_stride, const float* __restrict__ w, float eps,
@@ -73,7 +73,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
                     const float4 d = *reinterpret_cast<const float4*>(delta + s * split_stride + r * width + j);
                     v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
                 }
-                *reinterpret_cast<float4*>(xr + j) = v;
+                if (!rows) *reinterpret_cast<float4*>(xr + j) = v;      // (selected rows: x stays, see below)
             }
             *reinterpret_cast<float4*>(row + j) = v;
             ss = sumsq4(ss, v);
@@ -83,7 +83,7 @@ __global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ 
             float v = xr[j];
             if (delta) {
                 for (int s = 0; s < splits; ++s) v += delta[s * split_stride + r * width + j];
-                xr[j] = v;
+                if (!rows) xr[j] = v;
             }
             row[j] = v;
             ss += v * v;
@@ -152,7 +152,7 @@ __global__ void __launch_bounds__(128) rmsnorm_rows_kernel(float* __restrict__ x
 #pragma unroll
             for (int k = 0; k < KMAX; ++k) {
                 const int j = ((wv * 32 + lane) + k * VT) * 4;
-                if (j < width) *reinterpret_cast<float4*>(xr + j) = v[wv][k];
+                if (j < width && !rows) *reinterpret_cast<float4*>(xr + j) = v[wv][k];
             }
     }
     // the block kernel's sum: per thread over k, per warp by the butterfly, then over the warps by the butterfly

@@ -17,16 +17,15 @@ from typing import Dict, List, Optional, Sequence
 import numpy as np
 import torch
 
-PAGE = 64           # tokens per cache page
-Q_TILE = 64         # query rows per work item of the prompt attention kernels
+from ..layout import PAGE
 
 
 class BatchLayout:
     """Offsets (in int32 elements) of each field inside the packed buffer."""
 
-    def __init__(self, n_seqs: int, n_tokens: int, table_width: int, n_want: int, n_tiles: int):
+    def __init__(self, n_seqs: int, n_tokens: int, table_width: int, n_want: int):
         self.n_seqs, self.n_tokens, self.table_width = n_seqs, n_tokens, table_width
-        self.n_want, self.n_tiles = n_want, n_tiles
+        self.n_want = n_want
         off = 0
 
         def take(n: int) -> int:
@@ -44,8 +43,6 @@ class BatchLayout:
         self.slots = take(n_seqs)
         self.page_table = take(n_seqs * table_width)
         self.want = take(n_want)
-        self.tile_seq = take(n_tiles)
-        self.tile_q0 = take(n_tiles)
         self.size = off
 
 
@@ -61,7 +58,9 @@ class StepBatch:
     slots         int32 [n_seqs]     the cache slot (sequence record) of each sequence
     page_table    int32 [n_seqs, table_width]  page ids, in position order
     want          int32 [n_want]     flat token indices whose logits are returned
-    tile_seq/q0   int32 [n_tiles]    prompt attention work items: sequence and first query row
+
+    ``memo`` holds what parts compute once a step and share between layers (position
+    tables, a mixer's own work lists), under keys of their choosing.
     """
 
     def __init__(self, layout: BatchLayout, dev: torch.Tensor, *, q_lens: Sequence[int],
@@ -71,7 +70,7 @@ class StepBatch:
         self.layout = L
         self.buffer = dev
         self.n_seqs, self.n_tokens, self.table_width = L.n_seqs, L.n_tokens, L.table_width
-        self.n_want, self.n_tiles = L.n_want, L.n_tiles
+        self.n_want = L.n_want
         self.q_lens = list(q_lens)
         self.starts = list(starts)
         self.max_q_len = max(self.q_lens) if self.q_lens else 0
@@ -93,15 +92,9 @@ class StepBatch:
         self.slots = v(L.slots, L.n_seqs)
         self.page_table = v(L.page_table, L.n_seqs * L.table_width).view(L.n_seqs, L.table_width)
         self.want = v(L.want, L.n_want)
-        self.tile_seq = v(L.tile_seq, L.n_tiles)
-        self.tile_q0 = v(L.tile_q0, L.n_tiles)
         # Values that several layers share within the step (position tables and
         # the like), keyed by whoever computes them.
         self.memo: Dict[object, object] = {}
-
-
-def n_q_tiles(q_lens: Sequence[int]) -> int:
-    return sum((q + Q_TILE - 1) // Q_TILE for q in q_lens)
 
 
 def fill_host(layout: BatchLayout, out: np.ndarray, *, tokens: Sequence[Sequence[int]],
@@ -113,7 +106,6 @@ def fill_host(layout: BatchLayout, out: np.ndarray, *, tokens: Sequence[Sequence
     out[:] = 0
     t = 0
     w = 0
-    tile = 0
     pt = out[L.page_table:L.page_table + B * L.table_width].reshape(B, L.table_width)
     pt[:] = pad_page
     for b in range(B):
@@ -131,10 +123,6 @@ def fill_host(layout: BatchLayout, out: np.ndarray, *, tokens: Sequence[Sequence
         for i in want[b]:
             out[L.want + w] = t + i
             w += 1
-        for q0 in range(0, n, Q_TILE):
-            out[L.tile_seq + tile] = b
-            out[L.tile_q0 + tile] = q0
-            tile += 1
         t += n
     out[L.cu_seqlens + B] = t
-    assert t == L.n_tokens and w == L.n_want and tile == L.n_tiles
+    assert t == L.n_tokens and w == L.n_want

@@ -27,7 +27,7 @@ from ..config.base import ModelConfig, get_architecture, load_config
 from ..models.model import Model
 from ..weights.loader import load_weights
 from ..weights.random_init import random_fetch
-from .batch import BatchLayout, StepBatch, fill_host, n_q_tiles
+from .batch import BatchLayout, StepBatch, fill_host
 
 _DTYPES = {"bf16": torch.bfloat16, "bfloat16": torch.bfloat16, "f32": torch.float32, "float32": torch.float32,
            torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
@@ -87,7 +87,7 @@ class _Staging:
 class _DecodeGraph:
     def __init__(self, n_pad: int, table_width: int):
         self.n_pad, self.table_width = n_pad, table_width
-        self.layout = BatchLayout(n_pad, n_pad, table_width, n_pad, n_pad)
+        self.layout = BatchLayout(n_pad, n_pad, table_width, n_pad)
         self.buffer: Optional[torch.Tensor] = None
         self.batch: Optional[StepBatch] = None
         # What a batch that decodes on the device last wrote into the buffer (its slots and
@@ -239,7 +239,7 @@ class Engine:
         B = len(slots)
         kv_lens = [s + q for s, q in zip(starts, q_lens)]
         width = max(1, max((k + PAGE - 1) // PAGE for k in kv_lens))
-        layout = BatchLayout(B, sum(q_lens), width, sum(len(w) for w in want), n_q_tiles(q_lens))
+        layout = BatchLayout(B, sum(q_lens), width, sum(len(w) for w in want))
         pages = [cache.pages_of(s)[:(k + PAGE - 1) // PAGE] for s, k in zip(slots, kv_lens)]
         dev, _ = self._upload(layout, None, tokens=tokens, starts=starts, slots=slots, pages=pages, want=want)
         batch = StepBatch(layout, dev, q_lens=q_lens, starts=starts, workspace=self.workspace)

@@ -28,7 +28,7 @@ from typing import Callable, List, Optional, Sequence
 from ..sampling.sampler import Sampler, SamplerConfig
 from .run import StepRun
 
-PAGE = 64
+from ..layout import PAGE
 
 
 @dataclasses.dataclass

@@ -35,6 +35,10 @@ class Model:
             self.blocks.append(build_part("block", ls.block, ctx, mixer, mixer_norm, ffn, ffn_norm))
         self.final_norm = build_part("norm", spec.final_norm, ctx)
         self.head = build_part("head", spec.head, ctx)
+        named = {"embedding": self.embedding, "final_norm": self.final_norm, "head": self.head}
+        for _, part in self._places():
+            if part.PEERS:
+                part.attach({k: named[k] for k in part.PEERS})
         self.loaded = False
 
     # ---- tensors ---------------------------------------------------------
@@ -82,13 +86,10 @@ class Model:
         return any(fnmatch.fnmatchcase(name, pat) for pat in self.spec.ignore_tensors)
 
     def load(self, get: Callable[[str], Optional[torch.Tensor]]) -> None:
-        """``get(full_name)`` returns a tensor (any device) or None."""
+        """``get(full_name)`` returns a tensor (any device) or None.  Parts load in the order
+        embedding, layers, final norm, head."""
         for prefix, part in self._places():
-            fetch = (lambda p: (lambda local: get(p + local)))(prefix)
-            if part is self.head:
-                part.load(fetch, self.embedding)
-            else:
-                part.load(fetch)
+            part.load((lambda p: (lambda local: get(p + local)))(prefix))
         self.loaded = True
 
     # ---- sizes -------------------------------------------------------------

@@ -18,8 +18,7 @@ import torch
 
 from .build import BuildError, load_library
 
-PAGE = 64
-DECODE_SPLIT = 256
+from ..layout import PAGE
 
 
 class KernelError(RuntimeError):
@@ -46,6 +45,10 @@ class _Lib:
     def __init__(self, name, sources, defines=()):
         self._lib = load_library(name, sources, defines)
         self._fns: Dict[str, object] = {}
+        self._lib.wick_page_size.restype = ctypes.c_int
+        built_for = int(self._lib.wick_page_size())
+        if built_for != PAGE:
+            raise KernelError(f"{name} was built for cache pages of {built_for} positions, the package uses {PAGE}")
 
     def fn(self, name: str, sig: str):
         f = self._fns.get(name)
@@ -191,9 +194,10 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.
             out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """RMS norm of float32 ``x`` [n, width] into ``out_dtype``.
 
-    delta: float32 [splits, n, width]; added to ``x`` in place (for the rows that
-    are normalised) before the norm.  rows: int32 indices; only those rows are
-    normalised (and updated), the result has len(rows) rows."""
+    delta: float32 [splits, n, width]; added to ``x`` (in index order) before the norm,
+    and, when every row is normalised, in place.  rows: int32 indices (a row may be named
+    more than once); only those rows are normalised, the result has len(rows) rows, and
+    ``x`` itself is left as it was."""
     _cuda("x", x, torch.float32)
     n, width = x.shape
     _cuda("weight", weight, torch.float32, (width,))
@@ -313,6 +317,16 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, *, gated
 
 
 # ---------------------------------------------------------------------------
+Q_TILE = 64         # query rows per work item of the prompt attention kernels
+
+
+def attention_tiles(batch) -> int:
+    """How many work items the prompt attention kernels cut this step into: one per 64 new
+    tokens of a sequence, numbered sequence by sequence (a kernel finds its item's sequence
+    and first row from the step's ``cu_seqlens``)."""
+    return sum((q + Q_TILE - 1) // Q_TILE for q in batch.q_lens)
+
+
 def attention_prompt_kind(head_dim: int, dtype: torch.dtype, plain: bool = False) -> str:
     """Which prompt kernel runs: ``tc`` (tcgen05: bfloat16, head sizes 64 and 128),
     ``mma`` (mma.sync: bfloat16, other head sizes up to 128) or ``plain`` (CUDA
@@ -339,15 +353,15 @@ def attention_prompt(q: torch.Tensor, kv: torch.Tensor, batch, scale: float,
     _cuda("out", out, q.dtype, q.shape)
     kind = kind or attention_prompt_kind(hd, q.dtype, plain)
     _need(kind == "plain" or q.dtype == torch.bfloat16, "the tensor-core attention kernels take bfloat16")
+    n_tiles = attention_tiles(batch)
     if kind == "tc":
-        _attn(hd).call("wick_attn_prompt_tc_bf16", "plplpppipppiiifpp", _p(q), n, _p(kv), kv.shape[0], _p(out),
-                       _p(batch.tile_seq), _p(batch.tile_q0), batch.n_tiles, _p(batch.cu_seqlens), _p(batch.start),
+        _attn(hd).call("wick_attn_prompt_tc_bf16", "plplpipippiiifpp", _p(q), n, _p(kv), kv.shape[0], _p(out),
+                       n_tiles, _p(batch.cu_seqlens), batch.n_seqs, _p(batch.start),
                        _p(batch.page_table), batch.table_width, n_heads, n_kv, float(scale),
                        _p(status_tensor(q.device)), _stream())
         return out
-    _attn(hd).call("wick_attn_prompt_mma_bf16" if kind == "mma" else f"wick_attn_prompt_{_dt(q)}", "pppppipppiiifp",
-                   _p(q), _p(kv), _p(out), _p(batch.tile_seq),
-                   _p(batch.tile_q0), batch.n_tiles, _p(batch.cu_seqlens), _p(batch.start), _p(batch.page_table),
+    _attn(hd).call("wick_attn_prompt_mma_bf16" if kind == "mma" else f"wick_attn_prompt_{_dt(q)}", "pppipippiiifp",
+                   _p(q), _p(kv), _p(out), n_tiles, _p(batch.cu_seqlens), batch.n_seqs, _p(batch.start), _p(batch.page_table),
                    batch.table_width, n_heads, n_kv, float(scale), _stream())
     return out
 

@@ -85,10 +85,17 @@ class CacheNeed:
 
 class Part:
     category = ""
+    # Other places of the model whose part this one needs to see ("embedding", "final_norm",
+    # "head"): the model hands them over through :meth:`attach` before any weight is loaded.
+    # (An output head that shares the embedding table names "embedding".)
+    PEERS: Tuple[str, ...] = ()
 
     def __init__(self, params: Mapping[str, Any], ctx: BuildContext):
         self.params = dict(params)
         self.ctx = ctx
+
+    def attach(self, peers: Mapping[str, "Part"]) -> None:
+        """Receive the parts named in ``PEERS`` (place -> part)."""
 
     def tensor_specs(self) -> List[TensorSpec]:
         return []
@@ -122,7 +129,8 @@ class Norm(Part):
                     rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``x += sum(delta)`` in float32 and in place (``delta`` is
         [splits, n, width], summed in index order), then normalise.  With
-        ``rows`` only those rows need to be brought up to date."""
+        ``rows`` only those rows are normalised and ``x`` need not be brought up
+        to date (nobody reads it afterwards)."""
         x.add_(delta.sum(0) if delta.shape[0] > 1 else delta[0])
         return self.forward(x, out_dtype, rows)
 

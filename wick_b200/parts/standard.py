@@ -327,16 +327,23 @@ class LinearHead(Head):
         self.tied = bool(params.get("tied", False))
         self.linear = Linear(self.vocab, self.width, ctx)
         self.is_tied = self.tied
+        self.embedding: Optional[Embedding] = None
+
+    PEERS = ("embedding",)
+
+    def attach(self, peers):
+        self.embedding = peers.get("embedding")
 
     def tensor_specs(self):
         return [TensorSpec("weight", (self.vocab, self.width), optional=True)]
 
-    def load(self, fetch, embedding: Optional[TableEmbedding] = None):
+    def load(self, fetch):
         w = None if self.tied else fetch("weight")
         if w is None:
-            if embedding is None or embedding.weight is None:
-                raise ValueError("a tied head needs the embedding table")
-            self.linear.use(embedding.weight)
+            table = self.embedding.tensor("weight") if self.embedding is not None else None
+            if table is None:
+                raise ValueError("a tied head needs the embedding table (loaded before it)")
+            self.linear.use(table)
             self.is_tied = True
         else:
             self.linear.load_rows([w])
