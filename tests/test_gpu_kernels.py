@@ -593,3 +593,18 @@ def test_gemm_tensor_core_rows_do_not_depend_on_the_batch():
         assert torch.equal(part, full[:, :rows]), rows
     assert G.plan_for(dev(torch.zeros(64, 100, dtype=torch.bfloat16))) is None, "rows of 200 bytes cannot be fetched by TMA"
     assert G.plan_for(dev(torch.zeros(64, 96))) is None, "float32 weights take the CUDA-core kernel"
+
+
+def test_a_wait_that_nothing_satisfies_gives_up_and_is_reported(ops):
+    """Every ring kernel waits through the same bounded wait.  A kernel made for this test
+    (one block, one barrier that nobody arrives on, no copy in flight, a limit of one
+    millisecond) runs it out: the wait returns, the status word names it, the error is raised
+    once, and the device goes on working."""
+    ops.check_status()
+    assert ops.wait_gives_up(1.0) is True
+    with pytest.raises(ops.KernelError, match="gave up waiting for nothing"):
+        ops.check_status()
+    ops.check_status()                                       # the word was cleared
+    x = torch.randn(5, 72, device="cuda")
+    got = ops.rmsnorm(x, torch.ones(72, device="cuda"), 1e-6, torch.float32)
+    assert (got.cpu() - P.rms_norm(x.cpu(), torch.ones(72), 1e-6)).abs().max() < 1e-5

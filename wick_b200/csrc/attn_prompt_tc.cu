@@ -150,7 +150,7 @@ attn_prompt_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_co
                       float scale, int* status) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ uint64_t q_full, full[NSLOT];
-    __shared__ uint64_t s_full[NBUF], p_full[NBUF], pv_done[2], x_bar[4];   // pv_done: even blocks, odd blocks
+    __shared__ uint64_t s_full[NBUF], p_full[NBUF], pv_done[2], v_free[NBUF], x_bar[4];   // pv_done: even blocks, odd blocks
     __shared__ bf16 mx_x[2][2][BQ];                            // the maxima the two halves of a row tell each other
     __shared__ uint32_t tmem_slot;
     __shared__ int abort_flag;
@@ -185,6 +185,7 @@ attn_prompt_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_co
         }
         mbar_init(&pv_done[0], 1);
         mbar_init(&pv_done[1], 1);
+        for (int i = 0; i < NBUF; ++i) mbar_init(&v_free[i], 1);
         for (int i = 0; i < 4; ++i) mbar_init(&x_bar[i], 2);       // the two warps that share 32 rows
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -207,11 +208,14 @@ attn_prompt_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_co
             for (int i = 0; i < 2 * n_blk; ++i) {
                 const int slot = i % NSLOT, j = i >> 1, is_v = i & 1;
                 // The slot held the keys (values) of block j - 3: free when that block's scores are
-                // computed (its P V product is complete), which is what s_full (pv_done) says.
+                // computed (its P V product is complete), which is what s_full (v_free) says.  Each
+                // of these barriers completes one phase per visit of this thread, and its next phase
+                // needs the tile that is fetched after the wait: it can never be two phases on, which
+                // a parity could not tell from none.  (pv_done, which alternate blocks share, could:
+                // nothing holds the last two products back while this thread is late.)
                 if (j >= NBUF) {
                     const int jp = j - NBUF;
-                    if (!(is_v ? mbar_wait(&pv_done[jp & 1], (jp >> 1) & 1, &abort_flag, status, 7)
-                               : mbar_wait(&s_full[jp % NBUF], (jp / NBUF) & 1, &abort_flag, status, 7))) break;
+                    if (!mbar_wait(is_v ? &v_free[jp % NBUF] : &s_full[jp % NBUF], (jp / NBUF) & 1, &abort_flag, status, 7)) break;
                 }
                 mbar_expect_tx(&full[slot], TILE_BYTES);
                 for (int w = 0; w < 2; ++w) {
@@ -257,7 +261,8 @@ attn_prompt_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_co
                 if (j > 0) mma_ts<1>(d, pa, v_lo, idesc_o);
                 else mma_ts<0>(d, pa, v_lo, idesc_o);
                 static_for<1, BK / 16>([&](auto ks) { mma_ts<1>(d, pa + (int)ks * 8, v_lo + (int)ks * (2048 >> 4), idesc_o); });
-                tc_commit(&pv_done[j & 1]);                                  // (also: the values are read)
+                tc_commit(&pv_done[j & 1]);
+                tc_commit(&v_free[j % NBUF]);                                // the values are read: their tile is free
                 if (j + NBUF < n_blk) {
                     // the scores of block j + 3 go where this block's P lies: only when it has been read
                     ok = mbar_wait(&pv_done[j & 1], (j >> 1) & 1, &abort_flag, status, 7) && issue_s(j + NBUF);

@@ -32,8 +32,9 @@ __device__ __forceinline__ uint64_t global_ns() {
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
     return t;
 }
-// Bounded wait.  Returns false (and raises the block's abort flag) after ~1 s.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+// Bounded wait.  Returns false (and raises the block's abort flag) after limit_ns (~1 s).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code,
+                                          uint64_t limit_ns = 1000000000ull) {
     if (mbar_try_wait(bar, parity)) return true;         // the common case costs one instruction
     if (*abort_flag) return false;
     const uint64_t t0 = global_ns();
@@ -41,7 +42,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
         if (mbar_try_wait(bar, parity)) return true;
         if ((spin & 255u) == 255u) {
             if (*abort_flag) return false;
-            if (global_ns() - t0 > 1000000000ull) {
+            if (global_ns() - t0 > limit_ns) {
                 *abort_flag = 1;
                 if (status) atomicCAS(status, 0, code);
                 return false;

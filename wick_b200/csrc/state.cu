@@ -19,6 +19,7 @@
 // while it still rides along in a batch it runs its last step again and again,
 // which writes the same key and value to the same place and changes nothing.
 #include "common.cuh"
+#include "sm100.cuh"
 
 namespace wick {
 
@@ -144,9 +145,34 @@ __global__ void penalty_seen_kernel(float* logits, const uint8_t* __restrict__ s
     }
 }
 
+// A kernel whose only wait can never be satisfied: one block, one mbarrier that nothing
+// arrives on, no copy in flight.  It goes through the same bounded wait as every ring kernel
+// (sm100.cuh: mbar_wait), gives up after limit_ns, leaves its code in the status word and
+// returns.  It exists so that a test can see the give-up path end to end.
+__global__ void wait_gives_up_kernel(int* status, int code, uint64_t limit_ns, int* gave_up) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const bool ok = mbar_wait(&bar, 0, &abort_flag, status, code, limit_ns);
+        *gave_up = ok ? 0 : 1;
+    }
+}
+
 }  // namespace wick
 
 using namespace wick;
+
+WICK_API int wick_wait_gives_up(int* status, int code, long long limit_ns, int* gave_up, void* s) {
+    WICK_REQUIRE(limit_ns > 0 && limit_ns <= 100000000ll, "wait_gives_up: the limit must lie within 100 ms");
+    wait_gives_up_kernel<<<1, 32, 0, (cudaStream_t)s>>>(status, code, (uint64_t)limit_ns, gave_up);
+    return check_launch("wait_gives_up");
+}
 
 WICK_API int wick_seq_state_words() { return REC; }
 

@@ -115,7 +115,8 @@ _status: Optional[torch.Tensor] = None
 _STATUS_TEXT = {1: "gemm_tc: a free shared-memory stage", 2: "gemm_tc: a TMA copy", 3: "gemm_tc: the accumulator",
                 4: "attention decode: its bulk copies", 5: "gemm_tc: a free accumulator",
                 6: "attention decode (tensor cores): its TMA copies", 7: "attention (tcgen05): a copy or an accumulator",
-                8: "attention decode (fused): its TMA copies", 10: "attention decode: a page outside the cache"}
+                8: "attention decode (fused): its TMA copies", 10: "attention decode: a page outside the cache",
+                99: "nothing (the test kernel whose barrier nobody arrives on)"}
 
 
 def status_tensor(device) -> torch.Tensor:
@@ -670,3 +671,13 @@ def penalty_seen(logits: torch.Tensor, seen: torch.Tensor, state: torch.Tensor, 
     _cuda("slots", slots, torch.int32, (rows,))
     _core().call("wick_penalty_seen", "ppippfip", _p(logits), _p(seen), vocab, _p(state), _p(slots), float(penalty), rows,
                  _stream())
+
+
+def wait_gives_up(limit_ms: float = 1.0) -> bool:
+    """Run the kernel whose wait nothing can satisfy (one block, one barrier, no copies): its
+    bounded wait gives up after ``limit_ms`` and leaves code 99 in the status word, which
+    :func:`check_status` then reports.  Returns whether the wait gave up."""
+    st = status_tensor("cuda")
+    flag = torch.zeros(1, dtype=torch.int32, device=st.device)
+    _core().call("wick_wait_gives_up", "pilpp", _p(st), 99, int(limit_ms * 1e6), _p(flag), _stream())
+    return bool(flag.item())
