@@ -608,3 +608,106 @@ def test_a_wait_that_nothing_satisfies_gives_up_and_is_reported(ops):
     x = torch.randn(5, 72, device="cuda")
     got = ops.rmsnorm(x, torch.ones(72, device="cuda"), 1e-6, torch.float32)
     assert (got.cpu() - P.rms_norm(x.cpu(), torch.ones(72), 1e-6)).abs().max() < 1e-5
+
+
+def _decode_case(ops, heads, kv_heads, hd, lens, seed):
+    """Random cache contents for sequences of `lens` positions (the last one is the new
+    token, written by the norm/rotation/append kernel), scrambled pages, NaN wherever the
+    cache holds nothing.  Returns what the decode kernels and the plain attention need."""
+    torch.manual_seed(seed)
+    B = len(lens)
+    n_pages = sum((t + 63) // 64 for t in lens) + 1
+    perm = (torch.randperm(n_pages - 1) + 1).tolist()
+    pages, o = [], 0
+    for t in lens:
+        n = (t + 63) // 64
+        pages.append(perm[o:o + n])
+        o += n
+    kv = _paged(n_pages, kv_heads, hd, torch.bfloat16)
+    for b, t in enumerate(lens):
+        for i, pg in enumerate(pages[b]):
+            n = min(64, t - 1 - 64 * i)
+            if n > 0:
+                kv[pg, :, :, :n] = torch.randn(2, kv_heads, n, hd, device="cuda").bfloat16()
+    fd = FakeBatch([1] * B, [t - 1 for t in lens], pages).sb
+    width = (heads + 2 * kv_heads) * hd
+    parts = dev(torch.randn(3, B, width) * 0.6)
+    qw, kw = dev(1 + 0.1 * torch.randn(hd)), dev(1 + 0.1 * torch.randn(hd))
+    cos, sin = ops.rope_table(fd.positions, dev(P.rope_inv_freq(10000.0, hd)))
+    q = ops.qk_norm_rope_append(parts, heads, kv_heads, hd, q_weight=qw, k_weight=kw, eps=1e-6, cos=cos, sin=sin, kv=kv,
+                                page_table=fd.page_table, seq_of_token=fd.seq_of_token, positions=fd.positions,
+                                dtype=torch.bfloat16)
+    return q, kv, fd, pages
+
+
+def _plain_last_row(q_row, kv, pages_b, t, heads, kv_heads, scale):
+    kk = torch.cat([kv[pg, 0].float() for pg in pages_b], dim=1)[:, :t].transpose(0, 1).cpu()
+    vv = torch.cat([kv[pg, 1].float() for pg in pages_b], dim=1)[:, :t].transpose(0, 1).cpu()
+    qq = q_row.float().cpu()
+    g = heads // kv_heads
+    return torch.stack([P.softmax_rows(((qq[h] @ kk[:, h // g].T) * scale)[None])[0] @ vv[:, h // g] for h in range(heads)])
+
+
+def _run_parts(ops, q, kv, fd, heads, kv_heads, hd, max_kv_len=None):
+    mk = max_kv_len or fd.max_kv_len
+    scratch = torch.full((max(1, ops.attention_decode_parts_scratch(fd.n_seqs, heads, kv_heads, hd, mk)),), float("nan"),
+                         device="cuda")
+    out = ops.attention_decode_parts(q, kv, fd, 1 / math.sqrt(hd), scratch, max_kv_len=mk)
+    ops.check_status()
+    return out
+
+
+@pytest.mark.parametrize("heads, kv_heads, hd, lens", [
+    (8, 2, 128, (1, 130, 700, 64)), (4, 4, 64, (129, 5)), (16, 2, 128, (300,)), (6, 2, 64, (2000, 65, 128, 127, 1, 1025)),
+    (5, 1, 128, (4097, 4096, 4160, 3)), (8, 1, 64, (9000, 200)),
+    (8, 2, 128, _many_lengths(74, 1)), (6, 3, 64, _many_lengths(49, 2)), (8, 8, 128, _many_lengths(19, 3)),
+    (4, 1, 128, _many_lengths(300, 4)), (32, 8, 128, (1537,) * 24 + (1, 700, 1300, 128)),
+    (40, 8, 128, _many_lengths(16, 5)), (64, 8, 128, (1025,) * 8)])
+def test_decode_attention_by_parts(ops, heads, kv_heads, hd, lens):
+    """The tensor-core decode attention against the plain attention over the cache as it
+    stands: lengths around the 64-position page and the 128-position part, one part and many,
+    more than 64 pages (parts of more than two pages), groups of 1 to 8 query heads per kv
+    head (5 and 8: the shapes of Qwen3-14B and 32B), from one pair to 300, scrambled pages,
+    NaN wherever the cache holds no token and in the scratch."""
+    assert ops.attention_decode_parts_supported(len(lens), heads, kv_heads, hd, torch.bfloat16)
+    assert not ops.attention_decode_parts_supported(4, 18, 2, hd, torch.bfloat16), "9 query heads per kv head"
+    q, kv, fd, pages = _decode_case(ops, heads, kv_heads, hd, lens, hd + heads + len(lens))
+    before = torch.nan_to_num(kv.float(), nan=-7.0)
+    got = _run_parts(ops, q, kv, fd, heads, kv_heads, hd).float().cpu()
+    assert torch.isfinite(got).all()
+    scale = 1 / math.sqrt(hd)
+    check = range(len(lens)) if len(lens) <= 30 else list(range(0, len(lens), 7)) + [len(lens) - 1]
+    for b in check:
+        ref = _plain_last_row(q[b], kv, pages[b], lens[b], heads, kv_heads, scale)
+        assert (got[b] - ref).abs().max() < tol(torch.bfloat16, 1), f"sequence {b} of {lens[b]} positions"
+    assert torch.equal(torch.nan_to_num(kv.float(), nan=-7.0), before), "the cache is only read"
+    # a captured step sizes its work by the page table, not by the longest sequence: same bits
+    again = _run_parts(ops, q, kv, fd, heads, kv_heads, hd, max_kv_len=fd.table_width * 64).float().cpu()
+    assert torch.equal(again, got)
+
+
+@pytest.mark.parametrize("heads, kv_heads, hd", [(32, 8, 128), (8, 2, 64)])
+def test_decode_attention_bits_do_not_depend_on_the_batch(ops, heads, kv_heads, hd):
+    """A sequence's output rows are the same bits whether it is alone, among 8 or among 70
+    sequences (where its parts are computed by other warps, in another order in time)."""
+    lens = (1100, 3, 640, 77, 129, 2049, 64, 500) + _many_lengths(62, 9)
+    q, kv, fd, pages = _decode_case(ops, heads, kv_heads, hd, lens, 5)
+    full = _run_parts(ops, q, kv, fd, heads, kv_heads, hd)
+    for pick in ([0], [5], list(range(8)), [7, 0, 5]):
+        sub = FakeBatch([1] * len(pick), [lens[i] - 1 for i in pick], [pages[i] for i in pick]).sb
+        got = _run_parts(ops, q[pick].contiguous(), kv, sub, heads, kv_heads, hd)
+        assert torch.equal(got, full[pick]), pick
+
+
+def test_decode_attention_refuses_a_length_beyond_its_page_table(ops):
+    """A length that its page table cannot hold is left out and reported (status 10); nothing
+    outside the table or the cache is touched."""
+    heads, kv_heads, hd = 8, 2, 128
+    q, kv, fd, pages = _decode_case(ops, heads, kv_heads, hd, (200, 70), 3)
+    fd.kv_len[0] = fd.table_width * 64 + 1
+    scratch = torch.zeros(ops.attention_decode_parts_scratch(2, heads, kv_heads, hd, 4096), device="cuda")
+    out = ops.attention_decode_parts(q, kv, fd, 1 / math.sqrt(hd), scratch, max_kv_len=4096)
+    with pytest.raises(ops.KernelError, match="a page outside the cache"):
+        ops.check_status()
+    ref = _plain_last_row(q[1], kv, pages[1], 70, heads, kv_heads, 1 / math.sqrt(hd))
+    assert (out[1].float().cpu() - ref).abs().max() < tol(torch.bfloat16, 1), "the other sequence is served"

@@ -185,6 +185,19 @@ __device__ __forceinline__ T* fresh(T* p) {
     return p;
 }
 
+// Multiprocessors of the current device (asked once per process and device).
+inline int sm_count() {
+    static int per_device[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (per_device[dev] == 0) {                        // (two host threads may both ask; they store the same number)
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        per_device[dev] = n;
+    }
+    return per_device[dev];
+}
+
 inline bool pdl_enabled() {
     static int on = -1;
     if (on < 0) {

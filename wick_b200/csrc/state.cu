@@ -34,9 +34,12 @@ __global__ void seq_state_set_kernel(int* __restrict__ state, const int* __restr
     state[(int64_t)slots[i / REC] * REC + i % REC] = values[i];
 }
 
+// (This kernel never lets its successor start early: kernels further down the step read the
+// fields it writes, the lengths among them, before they wait for their own predecessor, as
+// they may with a description that the host has copied in.  With no early start here, every
+// kernel of the step begins after these fields are complete.)
 __global__ void step_prepare_kernel(const int* state, const int* __restrict__ slots, int* __restrict__ tokens,
                                     int* __restrict__ positions, int* __restrict__ start, int* __restrict__ kv_len, int n) {
-    pdl_trigger();
     pdl_wait();
     state = fresh(state);
     const int i = blockIdx.x * blockDim.x + threadIdx.x;

@@ -94,7 +94,7 @@ def _simt() -> _Lib:
 
 
 ATTN_SOURCES = ["attn.cu", "attn_decode.cu", "attn_decode_mma.cu", "attn_decode_fused.cu", "attn_decode_stream.cu",
-                "attn_prompt_mma.cu", "attn_prompt_tc.cu"]
+                "attn_decode_parts.cu", "attn_prompt_mma.cu", "attn_prompt_tc.cu"]
 
 
 def _attn(head_dim: int) -> _Lib:
@@ -104,7 +104,9 @@ def _attn(head_dim: int) -> _Lib:
         if head_dim % 16 != 0 or not 16 <= head_dim <= 256:
             raise KernelError(f"attention kernels take a head_dim that is a multiple of 16 between 16 and 256, "
                               f"not {head_dim}")
-        lib = _libs[key] = _Lib(f"wick_attn_hd{head_dim}", ATTN_SOURCES, [f"WICK_HD={head_dim}"])
+        # WICK_B200_ATTN_DEFINES: further -D definitions for experiments (e.g. "WICK_DECODE_WARPS=4,WICK_DECODE_TILES=3")
+        more = [d for d in os.environ.get("WICK_B200_ATTN_DEFINES", "").split(",") if d]
+        lib = _libs[key] = _Lib(f"wick_attn_hd{head_dim}", ATTN_SOURCES, [f"WICK_HD={head_dim}"] + more)
     return lib
 
 
@@ -434,6 +436,46 @@ def attention_decode(q: torch.Tensor, kv: torch.Tensor, batch, scale: float, scr
                        _p(scratch), scratch.numel(), _p(batch.kv_len), n, mk, _p(batch.page_table),
                        batch.table_width, n_heads, n_kv, float(scale), _p(status_tensor(q.device)), _stream(),
                        kernels=2)
+    return out
+
+
+def attention_decode_parts_supported(n_seqs: int, n_heads: int, n_kv: int, head_dim: int, dtype: torch.dtype) -> bool:
+    """Whether the tensor-core decode attention whose work is cut by each sequence's own
+    length takes this problem: bfloat16, head size 64 or 128, at most 8 query heads per kv head."""
+    if dtype != torch.bfloat16 or head_dim not in (64, 128) or n_kv <= 0 or n_heads % n_kv != 0 or n_heads // n_kv > 8:
+        return False
+    return n_seqs <= 2048
+
+
+def attention_decode_parts_scratch(n_seqs: int, n_heads: int, n_kv: int, head_dim: int, max_kv_len: int) -> int:
+    """float32 words of scratch that :func:`attention_decode_parts` needs."""
+    f = _attn(head_dim)._lib.wick_attn_decode_parts_scratch
+    f.restype = ctypes.c_longlong
+    f.argtypes = [ctypes.c_int] * 4
+    return int(f(n_seqs, n_heads, n_kv, max_kv_len))
+
+
+def attention_decode_parts(q: torch.Tensor, kv: torch.Tensor, batch, scale: float, scratch: torch.Tensor,
+                           out: Optional[torch.Tensor] = None, max_kv_len: Optional[int] = None) -> torch.Tensor:
+    """One new token per sequence over the cache (which already holds its key and value).
+    q: bfloat16 [n, heads, d].  scratch: float32, at least
+    :func:`attention_decode_parts_scratch` words.  How a sequence's positions are cut into
+    parts, and the order in which the parts are merged, depend on its own length only."""
+    _cuda("q", q, torch.bfloat16)
+    n, n_heads, hd = q.shape
+    _cuda("kv", kv, torch.bfloat16)
+    _need(kv.dim() == 5 and kv.shape[1] == 2 and kv.shape[3] == PAGE and kv.shape[4] == hd,
+          f"kv must be [pages, 2, kv_heads, {PAGE}, {hd}], is {tuple(kv.shape)}")
+    n_kv = kv.shape[2]
+    _need(n == batch.n_seqs, f"decode attention takes one token per sequence: {n} rows, {batch.n_seqs} sequences")
+    _cuda("scratch", scratch, torch.float32)
+    if out is None:
+        out = torch.empty_like(q)
+    _cuda("out", out, torch.bfloat16, q.shape)
+    mk = batch.max_kv_len if max_kv_len is None else max_kv_len
+    _attn(hd).call("wick_attn_decode_parts_bf16", "pplpplpiipiiifpp", _p(q), _p(kv), kv.shape[0], _p(out), _p(scratch),
+                   scratch.numel(), _p(batch.kv_len), n, mk, _p(batch.page_table), batch.table_width,
+                   n_heads, n_kv, float(scale), _p(status_tensor(q.device)), _stream(), kernels=2 if mk > 128 else 1)
     return out
 
 
