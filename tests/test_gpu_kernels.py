@@ -686,17 +686,82 @@ def test_decode_attention_by_parts(ops, heads, kv_heads, hd, lens):
     assert torch.equal(again, got)
 
 
-@pytest.mark.parametrize("heads, kv_heads, hd", [(32, 8, 128), (8, 2, 64)])
+@pytest.mark.parametrize("heads, kv_heads, hd, lens", [
+    (8, 2, 128, (1, 130, 700, 64)), (4, 4, 64, (129, 5)), (6, 2, 64, (2000, 65, 128, 127, 1, 1025)),
+    (5, 1, 128, (4097, 3)), (8, 8, 128, _many_lengths(19, 3)), (4, 1, 128, _many_lengths(300, 4)),
+    (32, 8, 128, (1537,) * 24 + (1, 700, 1300, 128)), (40, 8, 128, _many_lengths(16, 5)), (64, 8, 128, (1025,) * 8)])
+def test_decode_attention_by_parts_from_the_projections_sums(ops, heads, kv_heads, hd, lens):
+    """The form that starts from the q/k/v projection's float32 partial sums (sum, per-head norm,
+    rotation, the new key and value into the cache, attention) against the two kernels that do
+    the same in two steps: same output within the rounding of q, the same value row and (to
+    the last bfloat16 bit) key row in the cache and nothing else written; and with write_kv
+    off nothing is written and the cache's own row is used."""
+    torch.manual_seed(hd + heads + len(lens))
+    B = len(lens)
+    n_pages = sum((t + 63) // 64 for t in lens) + 1
+    perm = (torch.randperm(n_pages - 1) + 1).tolist()
+    pages, o = [], 0
+    for t in lens:
+        n = (t + 63) // 64
+        pages.append(perm[o:o + n])
+        o += n
+    kv_a = _paged(n_pages, kv_heads, hd, torch.bfloat16)
+    for b, t in enumerate(lens):
+        for i, pg in enumerate(pages[b]):
+            n = min(64, t - 1 - 64 * i)
+            if n > 0:
+                kv_a[pg, :, :, :n] = torch.randn(2, kv_heads, n, hd, device="cuda").bfloat16()
+    kv_b = kv_a.clone()
+    fd = FakeBatch([1] * B, [t - 1 for t in lens], pages).sb
+    sums = dev(torch.randn(3, B, (heads + 2 * kv_heads) * hd) * 0.6)
+    qw, kw = dev(1 + 0.1 * torch.randn(hd)), dev(1 + 0.1 * torch.randn(hd))
+    cos, sin = ops.rope_table(fd.positions, dev(P.rope_inv_freq(10000.0, hd)))
+    scale = 1 / math.sqrt(hd)
+    q = ops.qk_norm_rope_append(sums, heads, kv_heads, hd, q_weight=qw, k_weight=kw, eps=1e-6, cos=cos, sin=sin, kv=kv_a,
+                                page_table=fd.page_table, seq_of_token=fd.seq_of_token, positions=fd.positions,
+                                dtype=torch.bfloat16)
+    want = _run_parts(ops, q, kv_a, fd, heads, kv_heads, hd).float()
+    scratch = torch.full((max(1, ops.attention_decode_parts_scratch(B, heads, kv_heads, hd, fd.max_kv_len)),), float("nan"), device="cuda")
+    got = ops.attention_decode_parts_fused(sums, heads, kv_heads, hd, q_weight=qw, k_weight=kw, eps=1e-6, cos=cos, sin=sin,
+                                           kv=kv_b, batch=fd, scale=scale, scratch=scratch).float()
+    ops.check_status()
+    assert torch.isfinite(got).all()
+    assert (got - want).abs().max() < tol(torch.bfloat16, 1)
+    check = range(B) if B <= 30 else list(range(0, B, 11)) + [B - 1]
+    for b in check:
+        ref = _plain_last_row(q[b], kv_a, pages[b], lens[b], heads, kv_heads, scale)
+        assert (got[b].cpu() - ref).abs().max() < tol(torch.bfloat16, 1), f"sequence {b} of {lens[b]} positions"
+    for b, t in enumerate(lens):
+        page, row = pages[b][(t - 1) // 64], (t - 1) % 64
+        a, bb = kv_a[page, :, :, row].float(), kv_b[page, :, :, row].float()
+        assert torch.equal(a[1], bb[1]), "the value is the projection's sum, rounded once"
+        assert ((a[0] - bb[0]).abs() <= 2.0 ** -7 * a[0].abs() + 1e-30).all()
+        kv_b[page, 0, :, row] = kv_a[page, 0, :, row]
+    assert torch.equal(torch.nan_to_num(kv_b.float(), nan=-7.0), torch.nan_to_num(kv_a.float(), nan=-7.0))
+    kv_c = kv_a.clone()
+    again = ops.attention_decode_parts_fused(sums, heads, kv_heads, hd, q_weight=qw, k_weight=kw, eps=1e-6, cos=cos, sin=sin,
+                                             kv=kv_c, batch=fd, scale=scale, scratch=scratch, write_kv=False).float()
+    assert torch.equal(torch.nan_to_num(kv_c.float(), nan=-7.0), torch.nan_to_num(kv_a.float(), nan=-7.0))
+    assert (again - want).abs().max() < tol(torch.bfloat16, 1)
+
+
+@pytest.mark.parametrize("heads, kv_heads, hd", [(32, 8, 128), (8, 2, 64), (5, 1, 128)])
 def test_decode_attention_bits_do_not_depend_on_the_batch(ops, heads, kv_heads, hd):
     """A sequence's output rows are the same bits whether it is alone, among 8 or among 70
-    sequences (where its parts are computed by other warps, in another order in time)."""
+    sequences: alone and among few, a cluster of one-warp blocks computes its parts and merges
+    them through shared memory; among many, its parts are dealt to the warps of persistent
+    blocks and merged by a second kernel; and a captured step sizes everything by its page
+    table (more blocks per cluster than the sequence has parts)."""
     lens = (1100, 3, 640, 77, 129, 2049, 64, 500) + _many_lengths(62, 9)
     q, kv, fd, pages = _decode_case(ops, heads, kv_heads, hd, lens, 5)
     full = _run_parts(ops, q, kv, fd, heads, kv_heads, hd)
-    for pick in ([0], [5], list(range(8)), [7, 0, 5]):
+    for pick in ([0], [5], list(range(8)), [7, 0, 5], [2], [3, 4]):
         sub = FakeBatch([1] * len(pick), [lens[i] - 1 for i in pick], [pages[i] for i in pick]).sb
         got = _run_parts(ops, q[pick].contiguous(), kv, sub, heads, kv_heads, hd)
         assert torch.equal(got, full[pick]), pick
+        wide = FakeBatch([1] * len(pick), [lens[i] - 1 for i in pick], [pages[i] for i in pick], width=64).sb
+        got = _run_parts(ops, q[pick].contiguous(), kv, wide, heads, kv_heads, hd, max_kv_len=64 * 64)
+        assert torch.equal(got, full[pick]), (pick, "sized by a page table of 64 pages")
 
 
 def test_decode_attention_refuses_a_length_beyond_its_page_table(ops):

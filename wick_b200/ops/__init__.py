@@ -479,6 +479,40 @@ def attention_decode_parts(q: torch.Tensor, kv: torch.Tensor, batch, scale: floa
     return out
 
 
+def attention_decode_parts_fused(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, *,
+                                 q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
+                                 cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], kv: torch.Tensor, batch,
+                                 scale: float, scratch: torch.Tensor, write_kv: bool = True,
+                                 max_kv_len: Optional[int] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """:func:`attention_decode_parts` from the projection's float32 partial sums ``qkv``
+    [splits, n, (n_heads + 2 n_kv) head_dim]: per-head norm of q and k, rotation, the new key
+    and value into the cache (unless ``write_kv`` is False), attention, merge — two launches."""
+    _cuda("qkv", qkv, torch.float32)
+    width = (n_heads + 2 * n_kv) * head_dim
+    n = batch.n_seqs
+    _need(qkv.dim() == 3 and tuple(qkv.shape[1:]) == (n, width), f"qkv must be [splits, {n}, {width}], is {tuple(qkv.shape)}")
+    for nm, w in (("q_weight", q_weight), ("k_weight", k_weight)):
+        if w is not None:
+            _cuda(nm, w, torch.float32, (head_dim,))
+    _need((q_weight is None) == (k_weight is None), "q and k norm weights come together")
+    if cos is not None:
+        _cuda("cos", cos, torch.float32, (n, head_dim // 2))
+        _cuda("sin", sin, torch.float32, (n, head_dim // 2))
+    _cuda("kv", kv, torch.bfloat16)
+    _need(kv.dim() == 5 and tuple(kv.shape[1:]) == (2, n_kv, PAGE, head_dim),
+          f"kv must be [pages, 2, {n_kv}, {PAGE}, {head_dim}], is {tuple(kv.shape)}")
+    _cuda("scratch", scratch, torch.float32)
+    if out is None:
+        out = torch.empty((n, n_heads, head_dim), dtype=torch.bfloat16, device=qkv.device)
+    _cuda("out", out, torch.bfloat16, (n, n_heads, head_dim))
+    mk = batch.max_kv_len if max_kv_len is None else max_kv_len
+    _attn(head_dim).call("wick_attn_decode_parts_fused_bf16", "pippfppiplpplpiipiiifpp", _p(qkv), qkv.shape[0], _p(q_weight),
+                         _p(k_weight), float(eps), _p(cos), _p(sin), 1 if write_kv else 0, _p(kv), kv.shape[0], _p(out),
+                         _p(scratch), scratch.numel(), _p(batch.kv_len), n, mk, _p(batch.page_table), batch.table_width,
+                         n_heads, n_kv, float(scale), _p(status_tensor(qkv.device)), _stream(), kernels=2 if mk > 128 else 1)
+    return out
+
+
 _fused_ok: Dict[tuple, bool] = {}
 
 
