@@ -1,20 +1,12 @@
-"""The barrier protocol of the persistent decode attention kernels
-(csrc/attn_decode_mma.cu, csrc/attn_decode_stream.cu), simulated on the host with
-mbarrier semantics: a barrier completes a phase when its arrivals and its bytes
-are in, and a wait names the PARITY of the phase it waits for.
-
-Three stages, two pairs of warps; item n goes to stage n % 3 and to pair n % 2,
-so a pair meets a stage every sixth item.  With one set of barriers per stage a
-pair's wait lies two phases after its last one on that barrier, which a parity
-cannot tell from none: the protocol then holds only while copies complete in the
-order of their issue.  With barriers per (stage, pair) it holds under any order.
-The simulation runs the producer and the four compute warps under random
-interleavings and lets copies complete within a window of the oldest ones."""
+"""A model of the barrier protocol of the tcgen05 prompt attention (csrc/attn_prompt_tc.cu),
+run on the host with mbarrier semantics: a barrier completes a phase when its arrivals and
+its bytes are in, and a wait names the PARITY of the phase it waits for, so a barrier that is
+two phases on cannot be told from one that has not moved.  This is reasoning kept runnable, not
+a test of the kernel: the kernel itself is held against the plain attention in
+tests/test_gpu_kernels.py."""
 import random
 
 import pytest
-
-STAGES, GROUPS, PAGES = 3, 2, 2
 
 
 class Barrier:
@@ -38,113 +30,6 @@ class Barrier:
 
     def done(self, parity):                 # mbarrier.try_wait.parity
         return self.phase != parity
-
-
-def simulate(chunks, seed, window, per_pair):
-    """chunks[g]: how many chunks pair g consumes.  Raises AssertionError when a warp
-    reads a tile that is not its own, a barrier gets too many arrivals, or nothing moves."""
-    rnd = random.Random(seed)
-    dims = GROUPS if per_pair else 1
-    mk = lambda c: [[Barrier(c) for _ in range(dims)] for _ in range(STAGES)]
-    full_k, full_v, empty = mk(1), mk(1), mk(PAGES)
-    col = (lambda g: g) if per_pair else (lambda g: 0)
-    content = [dict() for _ in range(STAGES)]
-    inflight = []
-
-    def producer():
-        left, k, last = list(chunks), [0, 0], [None] * STAGES
-        n = 0
-        while left[0] > 0 or left[1] > 0:
-            g, s = n % GROUPS, n % STAGES
-            if per_pair:
-                if left[g] > 0:
-                    if last[s] is not None:
-                        lg, lm = last[s]
-                        while not empty[s][lg].done(lm & 1):
-                            yield
-                    last[s] = (g, n // (STAGES * GROUPS))
-            else:
-                rd = n // STAGES
-                while not empty[s][0].done((rd & 1) ^ 1):
-                    yield
-                if left[g] == 0:            # the pair has run out: the item passes through empty
-                    full_k[s][0].arrive()
-                    full_v[s][0].arrive()
-                    for _ in range(PAGES):
-                        empty[s][0].arrive()
-            if left[g] > 0:
-                full_k[s][col(g)].arrive(tx=1)
-                inflight.append((full_k[s][col(g)], s, "k", (g, k[g])))
-                full_v[s][col(g)].arrive(tx=1)
-                inflight.append((full_v[s][col(g)], s, "v", (g, k[g])))
-                k[g] += 1
-                left[g] -= 1
-            n += 1
-            yield
-
-    def warp(g, sync):
-        for k in range(chunks[g]):
-            n = GROUPS * k + g
-            s = n % STAGES
-            parity = ((n // (STAGES * GROUPS)) if per_pair else (n // STAGES)) & 1
-            while not full_k[s][col(g)].done(parity):
-                yield
-            assert content[s].get("k") == (g, k), f"pair {g} chunk {k} finds keys {content[s].get('k')}"
-            yield
-            while not full_v[s][col(g)].done(parity):
-                yield
-            assert content[s].get("v") == (g, k), f"pair {g} chunk {k} finds values {content[s].get('v')}"
-            yield
-            empty[s][col(g)].arrive()
-            sync[0] += 1                    # the pair's named barrier
-            while sync[0] < (k + 1) * PAGES:
-                yield
-
-    syncs = [[0], [0]]
-    threads = [producer()] + [warp(g, syncs[g]) for g in range(GROUPS) for _ in range(PAGES)]
-    alive, idle = list(range(len(threads))), 0
-    while alive:
-        if inflight and rnd.random() < 0.3:
-            bar, s, what, tag = inflight.pop(rnd.randrange(min(len(inflight), window)))
-            content[s] = dict(content[s])
-            content[s][what] = tag
-            bar.complete_tx(1)
-            idle = 0
-            continue
-        t = rnd.choice(alive)
-        try:
-            next(threads[t])
-        except StopIteration:
-            alive.remove(t)
-            idle = 0
-            continue
-        idle += 1
-        assert idle < 100000 or inflight, "nothing moves"
-
-
-CASES = [(26, 26), (26, 13), (13, 0), (10, 5), (5, 0), (1, 1), (3, 40), (0, 7)]
-
-
-@pytest.mark.parametrize("chunks", CASES)
-def test_barriers_per_stage_and_pair_hold_under_any_order_of_copies(chunks):
-    for seed in range(40):
-        simulate(chunks, seed, window=1000, per_pair=True)
-
-
-@pytest.mark.parametrize("chunks", CASES)
-def test_shared_barriers_hold_while_copies_complete_in_order(chunks):
-    for seed in range(25):
-        simulate(chunks, seed, window=1, per_pair=False)
-
-
-def test_shared_barriers_break_when_copies_may_overtake_each_other():
-    bad = 0
-    for seed in range(150):
-        try:
-            simulate((26, 26), seed, window=4, per_pair=False)
-        except AssertionError:
-            bad += 1
-    assert bad > 0, "a wait two phases after the last one cannot be told from none"
 
 
 # ---------------------------------------------------------------------------

@@ -421,8 +421,8 @@ WICK_API int wick_gemm_tc(const void* a, long long a_total_rows, int a_rows, con
     const long long total = (long long)p.grid_m * p.grid_n * splits;
     WICK_REQUIRE(total < (1ll << 30), "gemm_tc: too many tiles");
     p.total_tiles = (int)total;
-    // persistent blocks: as many as can be resident at once (148 SMs, one or two per SM by shared memory)
-    const int resident = 148 * ((smem + 12 * 1024) * 2 <= 227 * 1024 ? 2 : 1);
+    // persistent blocks: as many as can be resident at once (one or two per SM by shared memory)
+    const int resident = sm_count() * ((smem + 12 * 1024) * 2 <= 227 * 1024 ? 2 : 1);
     // Decode orientation (and anything that fits at once): one tile per block, so
     // that a block starting while others still stream overlaps their drain.
     // Prompt orientation with more tiles than resident blocks: persistent blocks.

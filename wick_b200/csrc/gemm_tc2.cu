@@ -358,7 +358,8 @@ WICK_API int wick_gemm_tc2(const void* a, int a_rows, const void* b, long long b
     p.split_stride = split_stride;
     WICK_REQUIRE(total * splits < (1ll << 30), "gemm_tc2: too many units");
     const int units = p.total_tiles * splits;
-    const int pairs = units < 74 ? units : 74;                       // 148 SMs
+    const int sm_pairs = sm_count() / 2;
+    const int pairs = units < sm_pairs ? units : sm_pairs;             // a pair of thread blocks per pair of SMs
     const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;
     if (gated) return out_f32 ? launch_pair<1, true, false>(map_a, map_b, p, 2 * pairs, smem, (cudaStream_t)stream)
                               : launch_pair<1, false, false>(map_a, map_b, p, 2 * pairs, smem, (cudaStream_t)stream);

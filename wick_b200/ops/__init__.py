@@ -93,8 +93,7 @@ def _simt() -> _Lib:
     return lib
 
 
-ATTN_SOURCES = ["attn.cu", "attn_decode.cu", "attn_decode_mma.cu", "attn_decode_fused.cu", "attn_decode_stream.cu",
-                "attn_decode_parts.cu", "attn_prompt_mma.cu", "attn_prompt_tc.cu"]
+ATTN_SOURCES = ["attn.cu", "attn_decode.cu", "attn_decode_parts.cu", "attn_prompt_mma.cu", "attn_prompt_tc.cu"]
 
 
 def _attn(head_dim: int) -> _Lib:
@@ -110,15 +109,16 @@ def _attn(head_dim: int) -> _Lib:
     return lib
 
 
-# One device word that kernels with bounded waits write a code to when a wait
-# gives up: 1-3 the tensor-core matrix product (a free stage, a TMA copy, the
-# accumulator), 4 decode attention (its bulk copies).
+# One device word that kernels write a code to when a bounded wait gives up or an index they
+# were given lies outside its table.
 _status: Optional[torch.Tensor] = None
-_STATUS_TEXT = {1: "gemm_tc: a free shared-memory stage", 2: "gemm_tc: a TMA copy", 3: "gemm_tc: the accumulator",
-                4: "attention decode: its bulk copies", 5: "gemm_tc: a free accumulator",
-                6: "attention decode (tensor cores): its TMA copies", 7: "attention (tcgen05): a copy or an accumulator",
-                8: "attention decode (fused): its TMA copies", 10: "attention decode: a page outside the cache",
-                99: "nothing (the test kernel whose barrier nobody arrives on)"}
+_STATUS_TEXT = {1: "gemm_tc gave up waiting for a free shared-memory stage", 2: "gemm_tc gave up waiting for a TMA copy",
+                3: "gemm_tc gave up waiting for the accumulator", 4: "attention decode gave up waiting for its bulk copies",
+                5: "gemm_tc gave up waiting for a free accumulator",
+                7: "attention (tcgen05) gave up waiting for a copy or an accumulator",
+                8: "attention decode (tensor cores) gave up waiting for its TMA copies",
+                10: "attention decode was given a length or a page outside its page table or its cache",
+                99: "the test kernel gave up waiting for nothing (nobody arrives on its barrier)"}
 
 
 def status_tensor(device) -> torch.Tensor:
@@ -134,8 +134,7 @@ def check_status() -> None:
         code = int(_status.item())
         if code != 0:
             _status.zero_()
-            raise KernelError(f"a kernel gave up waiting for {_STATUS_TEXT.get(code, 'code %d' % code)}; "
-                              f"its output is invalid")
+            raise KernelError(f"a kernel reported a fault: {_STATUS_TEXT.get(code, 'code %d' % code)}; its output is invalid")
 
 
 def _p(t: Optional[torch.Tensor]):
@@ -373,11 +372,10 @@ _decode_split: Dict[tuple, int] = {}
 
 
 def attention_decode_kind(head_dim: int, dtype: torch.dtype, plain: bool = False) -> str:
-    """Which decode kernel runs: ``mma`` (tensor cores: bfloat16, head sizes that are
-    64 or 128), ``fast`` (CUDA cores from bulk-copied tiles) or ``plain``."""
-    if plain:
-        return "plain"
-    return "mma" if dtype == torch.bfloat16 and head_dim in (64, 128) else "fast"
+    """Which of the CUDA-core decode kernels :func:`attention_decode` runs: ``fast`` (from
+    bulk-copied page tiles) or ``plain``.  (The tensor-core decode attention, bfloat16 at head
+    sizes 64 and 128, is :func:`attention_decode_parts`.)"""
+    return "plain" if plain else "fast"
 
 
 def attention_decode_split(head_dim: int, dtype: torch.dtype, plain: bool = False) -> int:
@@ -387,7 +385,7 @@ def attention_decode_split(head_dim: int, dtype: torch.dtype, plain: bool = Fals
     v = _decode_split.get(key)
     if v is None:
         lib = _attn(head_dim)._lib
-        name = {"plain": "wick_attn_decode_plain_split", "mma": "wick_attn_decode_mma_split",
+        name = {"plain": "wick_attn_decode_plain_split",
                 "fast": f"wick_attn_decode_split_{'bf16' if dtype == torch.bfloat16 else 'f32'}"}[kind]
         f = getattr(lib, name)
         f.restype = ctypes.c_int
@@ -405,10 +403,10 @@ def attention_decode_scratch_floats(n_seqs: int, n_heads: int, head_dim: int, ma
 def attention_decode(q: torch.Tensor, kv: torch.Tensor, batch, scale: float, scratch: torch.Tensor,
                      out: Optional[torch.Tensor] = None, max_kv_len: Optional[int] = None,
                      plain: bool = False) -> torch.Tensor:
-    """One new token per sequence.  scratch: float32, at least
-    :func:`attention_decode_scratch_floats` elements; it holds the per-split
-    partial results between the two kernels.  plain: the form without
-    shared-memory staging."""
+    """One new token per sequence, on the CUDA cores (float32, and bfloat16 at head sizes the
+    tensor-core kernel does not take).  scratch: float32, at least
+    :func:`attention_decode_scratch_floats` elements; it holds the per-split partial results
+    between the two kernels.  plain: the form without shared-memory staging."""
     _cuda("q", q)
     n, n_heads, hd = q.shape
     _cuda("kv", kv, q.dtype)
@@ -426,13 +424,8 @@ def attention_decode(q: torch.Tensor, kv: torch.Tensor, batch, scale: float, scr
         _attn(hd).call(f"wick_attn_decode_plain_{_dt(q)}", "pppplpiipiiifp", _p(q), _p(kv), _p(out),
                        _p(scratch), scratch.numel(), _p(batch.kv_len), n, mk, _p(batch.page_table),
                        batch.table_width, n_heads, n_kv, float(scale), _stream(), kernels=2)
-    elif kind == "fast":
-        _attn(hd).call(f"wick_attn_decode_{_dt(q)}", "pppplpiipiiifpp", _p(q), _p(kv), _p(out),
-                       _p(scratch), scratch.numel(), _p(batch.kv_len), n, mk, _p(batch.page_table),
-                       batch.table_width, n_heads, n_kv, float(scale), _p(status_tensor(q.device)), _stream(),
-                       kernels=2)
     else:
-        _attn(hd).call("wick_attn_decode_mma_bf16", "pplpplpiipiiifpp", _p(q), _p(kv), kv.shape[0], _p(out),
+        _attn(hd).call(f"wick_attn_decode_{_dt(q)}", "pppplpiipiiifpp", _p(q), _p(kv), _p(out),
                        _p(scratch), scratch.numel(), _p(batch.kv_len), n, mk, _p(batch.page_table),
                        batch.table_width, n_heads, n_kv, float(scale), _p(status_tensor(q.device)), _stream(),
                        kernels=2)
@@ -510,72 +503,6 @@ def attention_decode_parts_fused(qkv: torch.Tensor, n_heads: int, n_kv: int, hea
                          _p(k_weight), float(eps), _p(cos), _p(sin), 1 if write_kv else 0, _p(kv), kv.shape[0], _p(out),
                          _p(scratch), scratch.numel(), _p(batch.kv_len), n, mk, _p(batch.page_table), batch.table_width,
                          n_heads, n_kv, float(scale), _p(status_tensor(qkv.device)), _stream(), kernels=2 if mk > 128 else 1)
-    return out
-
-
-_fused_ok: Dict[tuple, bool] = {}
-
-
-def attention_decode_fused_supported(n_seqs: int, n_heads: int, n_kv: int, head_dim: int, dtype: torch.dtype) -> bool:
-    """Whether a one-kernel decode attention (q/k norm, rotation, cache append,
-    attention and merge in one launch) takes this problem: bfloat16, head size 64
-    or 128, at most 8 query heads per kv head.  (Two kernels: one that spreads a
-    (sequence, kv head) pair over a cluster of blocks, for as many pairs as run at
-    once, and one with persistent blocks for more.)"""
-    return _fused_kind(n_seqs, n_heads, n_kv, head_dim, dtype) is not None
-
-
-def _fused_kind(n_seqs: int, n_heads: int, n_kv: int, head_dim: int, dtype: torch.dtype) -> Optional[str]:
-    if dtype != torch.bfloat16 or head_dim not in (64, 128) or os.environ.get("WICK_B200_NO_FUSED_DECODE"):
-        return None
-    key = (n_seqs, n_heads, n_kv, head_dim)
-    if key not in _fused_ok:
-        kind = None
-        for name in ("fused", "stream"):
-            f = getattr(_attn(head_dim)._lib, f"wick_attn_decode_{name}_supported")
-            f.restype = ctypes.c_int
-            f.argtypes = [ctypes.c_int] * 3
-            if f(n_seqs, n_heads, n_kv) and not (name == "stream" and os.environ.get("WICK_B200_NO_STREAM_DECODE")):
-                kind = name
-                break
-        _fused_ok[key] = kind
-    return _fused_ok[key]
-
-
-def attention_decode_fused(qkv: torch.Tensor, n_heads: int, n_kv: int, head_dim: int, *,
-                           q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor], eps: float,
-                           cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], kv: torch.Tensor, batch,
-                           scale: float, write_kv: bool = True, max_kv_len: Optional[int] = None,
-                           out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """One new token per sequence, from the projection's float32 partial sums
-    ``qkv`` [splits, n, (n_heads + 2 n_kv) head_dim] to the attention output
-    [n, n_heads, head_dim] (bfloat16) in one launch: per-head norm of q and k,
-    rotation, the new key and value into the cache (unless ``write_kv`` is False),
-    attention over the cache, merge."""
-    _cuda("qkv", qkv, torch.float32)
-    width = (n_heads + 2 * n_kv) * head_dim
-    n = batch.n_seqs
-    _need(qkv.dim() == 3 and tuple(qkv.shape[1:]) == (n, width), f"qkv must be [splits, {n}, {width}], is {tuple(qkv.shape)}")
-    for nm, w in (("q_weight", q_weight), ("k_weight", k_weight)):
-        if w is not None:
-            _cuda(nm, w, torch.float32, (head_dim,))
-    _need((q_weight is None) == (k_weight is None), "q and k norm weights come together")
-    if cos is not None:
-        _cuda("cos", cos, torch.float32, (n, head_dim // 2))
-        _cuda("sin", sin, torch.float32, (n, head_dim // 2))
-    _cuda("kv", kv, torch.bfloat16)
-    _need(kv.dim() == 5 and tuple(kv.shape[1:]) == (2, n_kv, PAGE, head_dim),
-          f"kv must be [pages, 2, {n_kv}, {PAGE}, {head_dim}], is {tuple(kv.shape)}")
-    if out is None:
-        out = torch.empty((n, n_heads, head_dim), dtype=torch.bfloat16, device=qkv.device)
-    _cuda("out", out, torch.bfloat16, (n, n_heads, head_dim))
-    mk = batch.max_kv_len if max_kv_len is None else max_kv_len
-    kind = _fused_kind(n, n_heads, n_kv, head_dim, torch.bfloat16)
-    _need(kind is not None, f"no one-kernel decode attention for {n} sequences, {n_heads} heads over {n_kv} kv heads of {head_dim}")
-    _attn(head_dim).call(f"wick_attn_decode_{kind}_bf16", "piippfppplppipiiifipp", _p(qkv), qkv.shape[0], n, _p(q_weight),
-                         _p(k_weight), float(eps), _p(cos), _p(sin), _p(kv), kv.shape[0], _p(out), _p(batch.kv_len), mk,
-                         _p(batch.page_table), batch.table_width, n_heads, n_kv, float(scale), 1 if write_kv else 0,
-                         _p(status_tensor(qkv.device)), _stream())
     return out
 
 

@@ -32,7 +32,20 @@ SMALL = 64                  # up to this many tokens: weights as the 128-row ope
 SWAP_MAX = 255              # up to this many tokens: weights as the 128-row operand (measured: 5-14 % faster than
                             # tokens on the 128-row side for 100-200 tokens, whose one or two slabs leave SMs idle)
 PAIR_MIN = 256              # from this many tokens on, pairs of thread blocks share 256 x 256 tiles
-N_SMS = 148
+_sms = {}
+
+
+def sm_count(device) -> int:
+    """Multiprocessors of the device a weight lives on (148 on a B200; the same number for a
+    matrix that is not on a CUDA device, e.g. when only the plan's rules are looked at)."""
+    dev = torch.device(device)
+    if dev.type != "cuda":
+        return 148
+    n = _sms.get(dev)
+    if n is None:
+        n = _sms[dev] = torch.cuda.get_device_properties(dev).multi_processor_count
+    return n
+
 
 SOURCES = ["gemm_tc.cu", "gemm_tc2.cu"]
 
@@ -145,12 +158,13 @@ class Plan:
         self.rows, self.k = weight.shape
         self.n_out = self.rows // 2 if gated else self.rows
         self.w = pack(weight, gated)
+        self.sms = sm_count(weight.device)
         self.pair_offset = (self.n_out + 127) // 128 * 128            # in padded rows
         k_blocks = (self.k + 63) // 64
         tiles = (self.n_out + 127) // 128
-        # Decode: about two blocks per SM (just under 2 x 148) stream best; every
+        # Decode: about two blocks per SM (just under two per SM) stream best; every
         # split keeps at least eight 64-wide steps of the inner dimension.
-        self.decode_splits = max(1, min(2 * N_SMS // tiles, 8, k_blocks // 8))
+        self.decode_splits = max(1, min(2 * self.sms // tiles, 8, k_blocks // 8))
         self.k_blocks = k_blocks
 
     def matrix(self) -> torch.Tensor:
@@ -165,12 +179,12 @@ class Plan:
         if self.gated:
             return 1
         tiles = ((t + 255) // 256) * ((self.n_out + 255) // 256)
-        return max(1, min(4, (N_SMS // 2) // tiles, self.k_blocks // 32))
+        return max(1, min(4, (self.sms // 2) // tiles, self.k_blocks // 32))
 
     def short_prompt_splits(self) -> int:
         """Runs of the inner dimension for SMALL < tokens <= SWAP_MAX (weights as the 128-row
         operand, at most one block per SM)."""
-        return max(1, min(N_SMS // ((self.n_out + 127) // 128), 8, self.k_blocks // 8))
+        return max(1, min(self.sms // ((self.n_out + 127) // 128), 8, self.k_blocks // 8))
 
     def mid_splits(self, t: int) -> int:
         """Runs of the inner dimension when SWAP_MAX < ``t`` < PAIR_MIN tokens take the form with
@@ -180,7 +194,7 @@ class Plan:
         if self.gated:
             return 1
         tiles = ((t + 127) // 128) * ((self.n_out + 255) // 256)
-        return max(1, min(8, N_SMS // tiles, self.k_blocks // 8))
+        return max(1, min(8, self.sms // tiles, self.k_blocks // 8))
 
     # ---- [n, in] -> [n, out] ----
     def forward(self, x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:

@@ -25,7 +25,6 @@ output head ``src/model.rs:508-515`` with the tie rule of ``src/model.rs:190``.
 from __future__ import annotations
 
 import math
-import os
 from typing import Any, List, Mapping, Optional
 
 import torch
@@ -179,34 +178,17 @@ class GQAttention(Mixer):
             cos = sin = None
             if inv_freq is not None:
                 cos, sin = self.position.tables(batch)
-            mode = os.environ.get("WICK_B200_DECODE", "parts")
-            if batch.is_decode and mode in ("parts", "parts3") and ops.attention_decode_parts_supported(
+            if batch.is_decode and qkv.shape[0] <= 8 and ops.attention_decode_parts_supported(
                     batch.n_seqs, self.heads, self.kv_heads, self.head_dim, self.ctx.dtype):
+                # the tensor-core decode attention: the projection's sums, the q/k norm, the rotation,
+                # the cache append, the attention and the merge in one or two launches
                 need = ops.attention_decode_parts_scratch(batch.n_seqs, self.heads, self.kv_heads, self.head_dim, batch.kv_bound)
-                scratch = batch.workspace.get("attention_decode_parts", need, torch.float32)
-                qw = self.q_norm.weight if self.q_norm else None
-                kw = self.k_norm.weight if self.k_norm else None
-                eps = self.q_norm.eps if self.q_norm else 0.0
-                if mode == "parts" and qkv.shape[0] <= 8:
-                    att = ops.attention_decode_parts_fused(
-                        qkv, self.heads, self.kv_heads, self.head_dim, q_weight=qw, k_weight=kw, eps=eps, cos=cos, sin=sin,
-                        kv=cache.kv, batch=batch, scale=self.scale, scratch=scratch, write_kv=write_cache,
-                        max_kv_len=batch.kv_bound)
-                else:
-                    q = ops.qk_norm_rope_append(
-                        qkv, self.heads, self.kv_heads, self.head_dim, q_weight=qw, k_weight=kw, eps=eps, cos=cos, sin=sin,
-                        kv=cache.kv, page_table=batch.page_table, seq_of_token=batch.seq_of_token,
-                        positions=batch.positions, write_kv=write_cache, dtype=self.ctx.dtype)
-                    att = ops.attention_decode_parts(q, cache.kv, batch, self.scale, scratch, max_kv_len=batch.kv_bound)
-                return self.o.forward_delta(att.view(batch.n_tokens, self.q_dim), residual)
-            if batch.is_decode and qkv.shape[0] <= 8 and ops.attention_decode_fused_supported(batch.n_seqs, self.heads, self.kv_heads,
-                                                                        self.head_dim, self.ctx.dtype):
-                att = ops.attention_decode_fused(
-                    qkv, self.heads, self.kv_heads, self.head_dim,
-                    q_weight=self.q_norm.weight if self.q_norm else None,
-                    k_weight=self.k_norm.weight if self.k_norm else None,
-                    eps=self.q_norm.eps if self.q_norm else 0.0, cos=cos, sin=sin, kv=cache.kv, batch=batch,
-                    scale=self.scale, write_kv=write_cache, max_kv_len=batch.kv_bound)
+                att = ops.attention_decode_parts_fused(
+                    qkv, self.heads, self.kv_heads, self.head_dim, q_weight=self.q_norm.weight if self.q_norm else None,
+                    k_weight=self.k_norm.weight if self.k_norm else None, eps=self.q_norm.eps if self.q_norm else 0.0,
+                    cos=cos, sin=sin, kv=cache.kv, batch=batch, scale=self.scale,
+                    scratch=batch.workspace.get("attention_decode_parts", need, torch.float32), write_kv=write_cache,
+                    max_kv_len=batch.kv_bound)
                 return self.o.forward_delta(att.view(batch.n_tokens, self.q_dim), residual)
             q = ops.qk_norm_rope_append(
                 qkv, self.heads, self.kv_heads, self.head_dim,
