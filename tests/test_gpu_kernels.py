@@ -699,3 +699,26 @@ def test_decode_attention_refuses_a_length_beyond_its_page_table(ops):
         ops.check_status()
     ref = _plain_last_row(q[1], kv, pages[1], 70, heads, kv_heads, 1 / math.sqrt(hd))
     assert (out[1].float().cpu() - ref).abs().max() < tol(torch.bfloat16, 1), "the other sequence is served"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_cuda_core_decode_attention_cuts_a_length_back_to_its_table(ops, dtype):
+    """A length one split beyond what the call was sized for: the kernel reports it and works
+    on what the page table and the scratch hold (the cache and the table given here are large
+    enough that even an unguarded kernel would have stayed inside them)."""
+    heads, kv_heads, hd = 4, 2, 32
+    split = ops.attention_decode_split(hd, dtype)
+    n = 2 * split
+    torch.manual_seed(1)
+    kv = torch.randn(2 * n // 64 + 2, 2, kv_heads, 64, hd, device="cuda").to(dtype)
+    q = torch.randn(1, heads, hd, device="cuda").to(dtype)
+    pages = [list(range(1, 2 * n // 64 + 1))]
+    fd = FakeBatch([1], [n + split - 1], pages, width=2 * n // 64).sb        # kv_len = n + split
+    scratch = torch.zeros(4 * ops.attention_decode_scratch_floats(1, heads, hd, n + split, dtype), device="cuda")
+    out = ops.attention_decode(q, kv, fd, 1 / math.sqrt(hd), scratch, max_kv_len=n)
+    with pytest.raises(ops.KernelError, match="outside its page table"):
+        ops.check_status()
+    fd_ok = FakeBatch([1], [n - 1], pages, width=2 * n // 64).sb
+    want = ops.attention_decode(q, kv, fd_ok, 1 / math.sqrt(hd), scratch, max_kv_len=n)
+    ops.check_status()
+    assert torch.equal(out, want), "the first max_kv_len positions were attended to"

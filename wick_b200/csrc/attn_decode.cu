@@ -56,7 +56,14 @@ attn_decode_fast_kernel(const T* __restrict__ q, const T* __restrict__ kv, float
     q = fresh(q);
     kv = fresh(kv);
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
-    const int kv_len = kv_len_arr[b];
+    // A length beyond what the page table or the scratch (max_splits) holds is cut back to it
+    // and reported: nothing outside the table or the scratch is touched.
+    const int most = min(table_width * kPage, max_splits * SPLIT);
+    int kv_len = kv_len_arr[b];
+    if (kv_len > most) {
+        if (split == 0 && kvh == 0 && threadIdx.x == 0 && status) atomicCAS(status, 0, 10);
+        kv_len = most;
+    }
     const int key_begin = split * SPLIT;
     if (key_begin >= kv_len) return;
     const int group = n_heads / n_kv;
@@ -238,7 +245,7 @@ __global__ void attn_decode_fast_merge_kernel(const float* __restrict__ part_o, 
     part_o = fresh(part_o);
     part_ml = fresh(part_ml);
     const int head = blockIdx.x, b = blockIdx.y;
-    const int n_splits = (kv_len_arr[b] + SPLIT - 1) / SPLIT;
+    const int n_splits = min((kv_len_arr[b] + SPLIT - 1) / SPLIT, max_splits);   // (a longer length was cut back and reported)
     const int64_t row0 = ((int64_t)b * n_heads + head) * max_splits;
     float m = -INFINITY;
     for (int s = 0; s < n_splits; ++s) m = fmaxf(m, part_ml[(row0 + s) * 2]);
@@ -290,7 +297,8 @@ WICK_API int wick_attn_decode_split_bf16() { return fastdecode::Shape<bf16>::SPL
 WICK_API int wick_attn_decode_split_f32() { return fastdecode::Shape<float>::SPLIT; }
 
 // q, out: [n_seqs, n_heads, HD]; kv: one schedule entry's cache.  status: device
-// int that receives 4 if a block gave up waiting for its copies.
+// int that receives 4 if a block gave up waiting for its copies, 10 if a length was beyond the
+// page table or max_kv_len (it is then cut back to what they hold).
 WICK_API int wick_attn_decode_bf16(const void* q, const void* kv, void* out, float* scratch, int64_t scratch_floats,
                                    const int* kv_len, int n_seqs, int max_kv_len, const int* page_table,
                                    int table_width, int n_heads, int n_kv, float scale, int* status, void* s) {
@@ -334,6 +342,8 @@ constexpr long long kNoAllocFloats = 2ll * 1024 * 1024;
 static __device__ __align__(256) float g_noalloc_scratch[kNoAllocFloats];
 
 static int noalloc_scratch(float** out) {
+    // (No lock: two host threads may both look the symbol up on a device's first call; they
+    // store the same address.)
     static float* per_device[64] = {};
     int dev = -1;
     WICK_CUDA(cudaGetDevice(&dev));
