@@ -463,3 +463,20 @@ def test_four_layers_at_the_real_sizes_of_qwen3_8b_in_float32():
     want = torch.cat([ref[[0, 150, 299]], ref[300:]])
     assert_logits_close(torch.cat(got), want, "float32", "four real layers")
     eng.check_kernels()
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_the_kernels_status_word_is_read_now_and_then(graphs, monkeypatch):
+    """Replayed steps count like launched ones: every 64 steps the status word is read, so a
+    kernel that gave up a wait cannot go unnoticed for long."""
+    from wick_b200 import ops
+    eng = make_engine("A", "float32", use_graphs=graphs)
+    s = eng.open_seq()
+    eng.step([s], [[1, 2, 3]])
+    calls = []
+    real = ops.check_status
+    monkeypatch.setattr(ops, "check_status", lambda: (calls.append(1), real())[1])
+    for t in range(130):
+        eng.step([s], [[t % 500]])
+    assert len(calls) >= 2
+    eng.close_seq(s)
