@@ -226,6 +226,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--prompt-len", type=int, default=PROMPT, help="tokens of each prompt before the timed decode steps")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL, help="tokens of the prefill step (the contract's is 2,048)")
     ap.add_argument("--repeats", type=int, default=REPEATS, help="timed regions of --steps decode steps each (median reported)")
     ap.add_argument("--skip-points", action="store_true", help="no batch 1 / 64 runs")
     ap.add_argument("--skip-models", action="store_true", help="no 14b / 32b workloads")
@@ -263,7 +264,8 @@ def main() -> int:
     cfg = wick.config_from_json(cfg_json)
     max_batch = max(args.batch, 1 if args.skip_points else 64)
     per_seq = (args.prompt_len + warmup + repeats * steps + 2 + 64 + 63) // 64 * 64
-    max_tokens = max(max_batch * per_seq, PREFILL + 64)
+    n_prefill = args.prefill_tokens
+    max_tokens = max(max_batch * per_seq, n_prefill + 64)
     t0 = time.time()
     eng = wick.Engine.from_config(cfg, seed=0, dtype="bfloat16", max_tokens=max_tokens,
                                   use_graphs=False if args.eager else None)
@@ -313,7 +315,7 @@ def main() -> int:
         d2h = (args.batch + 1) * 4
 
     # ---- prefill of one 2,048-token prompt ----
-    ptoks = random_prompts(torch, vocab, [PREFILL], 3)[0]
+    ptoks = random_prompts(torch, vocab, [n_prefill], 3)[0]
     times = []
     for i in range(0 if args.skip_prefill else 2 + 3):
         s = eng.open_seq()
@@ -330,9 +332,9 @@ def main() -> int:
     pms = statistics.median(times) if times else float("nan")
     c = cfg
     gemm_params = len(eng.spec.schedule) * (c.hidden_size * (2 * c.q_dim + 2 * c.kv_dim) + 3 * c.hidden_size * c.intermediate_size)
-    flops = 2.0 * PREFILL * gemm_params + 2.0 * vocab * c.hidden_size            # head on one row
-    flops += len(eng.spec.schedule) * 4.0 * c.num_attention_heads * c.head_dim * PREFILL * (PREFILL + 1) / 2
-    prefill = {"value": PREFILL / (pms * 1e-3), "tokens": PREFILL, "ms": pms,
+    flops = 2.0 * n_prefill * gemm_params + 2.0 * vocab * c.hidden_size            # head on one row
+    flops += len(eng.spec.schedule) * 4.0 * c.num_attention_heads * c.head_dim * n_prefill * (n_prefill + 1) / 2
+    prefill = {"value": n_prefill / (pms * 1e-3), "tokens": n_prefill, "ms": pms,
                "frac": flops / (pms * 1e-3) / 1e12 / pk["bf16_tflops_sustained"],
                "tflops": flops / (pms * 1e-3) / 1e12, "peak_tflops": pk["bf16_tflops_sustained"],
                "ms_min": min(times) if times else None, "ms_max": max(times) if times else None}

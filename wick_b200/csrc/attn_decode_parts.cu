@@ -197,8 +197,8 @@ struct Projection {
     int write_kv;
 };
 
-// PAIR: the form for few pairs of short parts (no more pairs than SMs, sequences of up to 16
-// pages).  A block takes one pair and its warps the pair's parts; the block makes the new
+// PAIR: the form for few pairs (up to some 400; fewer for long sequences: the host decides by
+// measured rules).  A block takes one pair and its warps the pair's parts; the block makes the new
 // token's rows once, all warps at it (a row or two each, one trip to the L2 cache), and when
 // all parts are done its warps merge the pair's records, a head each: one launch.  Otherwise
 // (persistent form) all parts of the step are dealt to the warps of one block per SM, and the
@@ -749,7 +749,11 @@ static int launch_parts(bool prep, const void* q, decodeparts::Projection proj, 
     // number of pairs, until the SMs that have a pair cannot keep the memory busy between them; the persistent
     // form costs about 9 us + the step's bytes at 5 TB/s.
     const bool pays = pages <= 16 || pairs >= 96 || (pairs >= 24 && pages <= 24) || (pairs >= 48 && pages <= 32);
-    const bool pair_form = pairs <= sms && (force >= 0 ? force == 1 : pays);
+    // More pairs than SMs, up to some 400: the blocks run in waves; that still beats the persistent form, whose
+    // warps then have one or two parts each, unless the last wave is mostly empty.
+    const long long waves = (pairs + sms - 1) / sms;
+    const bool waves_pay = pairs <= 400 && pairs * 10 >= waves * sms * 6;
+    const bool pair_form = force >= 0 ? force == 1 : (pairs <= sms ? pays : waves_pay);
     if (pair_form) {
         // Few pairs of short parts: a block per pair, its warps at the pair's parts, merged by the block itself.
         // (Longer parts, or more pairs than SMs, want the self-fed warps of the persistent form.)
