@@ -39,15 +39,19 @@ CONFIG_D = dict(architectures=["Qwen3ForCausalLM"], hidden_size=128, num_attenti
 # step is short, so a captured step overlaps each kernel with the end of the one
 # before it as far as programmatic dependent launch allows.
 CONFIG_E = dict(architectures=["Qwen3ForCausalLM"], hidden_size=256, num_attention_heads=4, num_key_value_heads=1,
-                head_dim=128, intermediate_size=384, num_hidden_layers=2, vocab_size=1003, max_position_embeddings=2048,
+                head_dim=128, intermediate_size=384, num_hidden_layers=2, vocab_size=1003, max_position_embeddings=8192,
                 rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=True)
+# F: a group of 5 query heads per kv head at head_dim 128 (the grouping of Qwen3-14B), two kv heads.
+CONFIG_F = dict(architectures=["Qwen3ForCausalLM"], hidden_size=320, num_attention_heads=10, num_key_value_heads=2,
+                head_dim=128, intermediate_size=448, num_hidden_layers=2, vocab_size=777, max_position_embeddings=2048,
+                rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False)
 # R: one layer with the real widths of Qwen3-8B (hidden 4096, 32 heads over 8 kv
 # heads of 128, intermediate 12288) and a vocabulary that is no multiple of the
 # kernels' tile sizes.
 CONFIG_R = dict(architectures=["Qwen3ForCausalLM"], hidden_size=4096, num_attention_heads=32, num_key_value_heads=8,
                 head_dim=128, intermediate_size=12288, num_hidden_layers=1, vocab_size=20011,
                 max_position_embeddings=4096, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=False)
-CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "D": CONFIG_D, "E": CONFIG_E, "R": CONFIG_R}
+CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "D": CONFIG_D, "E": CONFIG_E, "F": CONFIG_F, "R": CONFIG_R}
 
 _tmp_root = None
 

@@ -480,3 +480,26 @@ def test_the_kernels_status_word_is_read_now_and_then(graphs, monkeypatch):
         eng.step([s], [[t % 500]])
     assert len(calls) >= 2
     eng.close_seq(s)
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_group_of_five_query_heads_per_kv_head(dtype, graphs):
+    """Config F: 10 heads over 2 kv heads of 128 (the grouping of Qwen3-14B): unequal prompts,
+    then decoding, the shorter requests leaving earlier."""
+    name = "F"
+    eng = make_engine(name, dtype, max_tokens=4096, use_graphs=graphs)
+    poison_all(eng)
+    _run_batch_against_plain(name, dtype, eng, (130, 1, 700, 64, 300), (12, 5, 12, 3, 9), 6000)
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_decoding_beyond_64_pages(dtype, graphs):
+    """A 4,150-token prompt (33 blocks of 128 keys in the prompt attention) and a 70-token one,
+    then 10 decoded tokens each: beyond 64 pages the decode attention's parts grow from two
+    pages to four, and the captured step is made for a page table of 128 pages."""
+    name = "E"
+    eng = make_engine(name, dtype, max_tokens=8192, use_graphs=graphs)
+    poison_all(eng)
+    _run_batch_against_plain(name, dtype, eng, (4150, 70), (10, 10), 7000, every=3)
