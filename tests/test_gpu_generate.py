@@ -164,8 +164,9 @@ def test_a_batch_stepped_on_the_device_gives_the_tokens_of_the_stepwise_loop(nam
         assert eng.cache.pages.n_held == 0 and eng.cache.slots.n_held == 0
 
 
-def test_steady_decoding_uploads_nothing():
-    eng = make_engine("D", "bfloat16", std=STD, max_tokens=64 * 16)
+@pytest.mark.parametrize("graphs", [True, False])
+def test_steady_decoding_uploads_nothing(graphs):
+    eng = make_engine("D", "bfloat16", std=STD, max_tokens=64 * 16, use_graphs=graphs)
     prompts = [random_tokens(640, n, 500 + n) for n in (30, 5, 11)]
     runs = []
     begin = eng.begin_run

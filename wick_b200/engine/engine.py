@@ -262,9 +262,10 @@ class Engine:
             b *= 2
         return b
 
-    def _decode_graph(self, n_seqs: int, max_pages: int) -> _DecodeGraph:
+    def _decode_graph(self, n_seqs: int, max_pages: int, capture: bool = True) -> _DecodeGraph:
         """The captured step for ``n_seqs`` sequences (padded to a power of two) whose page
-        tables hold up to ``max_pages`` pages (padded to 8, 16, 32 ...); captured on first use."""
+        tables hold up to ``max_pages`` pages (padded to 8, 16, 32 ...); captured on first use
+        (``capture`` False: only its buffer and batch description are made)."""
         n_pad = self._bucket(n_seqs)
         width = 8
         while width < max_pages:
@@ -276,7 +277,7 @@ class Engine:
             g.buffer = torch.zeros(g.layout.size, dtype=torch.int32, device=self.device)
             g.batch = StepBatch(g.layout, g.buffer, q_lens=[1] * n_pad, starts=[0] * n_pad, workspace=self.workspace,
                                 kv_bound=width * PAGE)
-        if g.graph is None:
+        if g.graph is None and capture:
             # Capture (and its warm-up run) on a batch of padding entries only, so
             # that no live sequence's cache or state is touched twice.
             self._upload(g.layout, g.buffer, tokens=[[0]] * n_pad, starts=[0] * n_pad, slots=[0] * n_pad,

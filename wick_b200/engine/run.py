@@ -136,7 +136,7 @@ class DeviceRun:
             n = cache.length(s) + 1
             cache.reserve(s, n)
             longest = max(longest, n)
-        g = e._decode_graph(B, (longest + PAGE - 1) // PAGE)
+        g = e._decode_graph(B, (longest + PAGE - 1) // PAGE, capture=e.use_graphs)
         composition = (tuple(slots), tuple(len(cache.pages_of(s)) for s in slots))
         if g.composition != composition:
             # (token, position and lengths of the description are written by step_prepare)
@@ -147,9 +147,14 @@ class DeviceRun:
         b = g.batch
         with ops.stream_scope():
             ops.step_prepare(e.seq_state, b.slots, b.tokens, b.positions, b.start, b.kv_len)
-            g.graph.replay()
-            ops.launches[0] += g.kernels
-            self._sample_and_advance(g.logits[:B], b.slots[:B], b.kv_len[:B], B)
+            if e.use_graphs:
+                g.graph.replay()
+                ops.launches[0] += g.kernels
+                logits = g.logits
+            else:                                        # (graphs switched off: the same step as separate launches)
+                b.memo.clear()
+                logits = e.model.forward(b, cache)
+            self._sample_and_advance(logits[:B], b.slots[:B], b.kv_len[:B], B)
         for s in slots:
             cache.advance(s, 1)
 
