@@ -207,3 +207,25 @@ def test_the_models_own_stop_tokens_end_a_sequence(dtype):
     else:
         assert 7 not in out.tokens and 9 not in out.tokens
         assert out.finish == "stop" or len(out.tokens) == 12
+
+
+def test_a_shrinking_batch_that_ends_soon_keeps_its_captured_step():
+    """Five requests that end at different times: the batch shrinks from 5 (a captured step of
+    8) to 1, but all of them end within 64 steps, so no smaller step is captured on the way:
+    one captured step serves the whole batch.  A generation that goes on for long captures the
+    step of its own size."""
+    eng = make_engine("D", "bfloat16", std=STD, max_tokens=64 * 40)
+    prompts = [random_tokens(640, n, 800 + n) for n in (12, 5, 30, 7, 3)]
+    base = wick.GenOptions(max_tokens=30, sampler=wick.SamplerConfig.greedy())
+    free = wick.generate(eng, prompts, base, sampler_factory=wick.Sampler)
+    stops = [free[0].tokens[3], free[1].tokens[8], free[3].tokens[14]]
+    opts = wick.GenOptions(max_tokens=30, sampler=wick.SamplerConfig.greedy(), stop_token_ids=stops)
+    want = wick.generate(eng, prompts, opts, sampler_factory=wick.Sampler)
+    eng2 = make_engine("D", "bfloat16", std=STD, max_tokens=64 * 40)
+    got = wick.generate(eng2, prompts, opts)
+    assert [(r.tokens, r.finish) for r in got] == [(r.tokens, r.finish) for r in want]
+    assert len({len(r.tokens) for r in got}) > 2, "the requests end at different times"
+    captured = sorted(k for k, g in eng2._graphs.items() if g.graph is not None)
+    assert captured == [(8, 8)], captured
+    long = wick.generate(eng2, [prompts[0]], wick.GenOptions(max_tokens=200, sampler=wick.SamplerConfig.greedy()))
+    assert len(long[0].tokens) == 200 and (1, 8) in {k for k, g in eng2._graphs.items() if g.graph is not None}

@@ -262,7 +262,7 @@ class Engine:
             b *= 2
         return b
 
-    def _decode_graph(self, n_seqs: int, max_pages: int, capture: bool = True) -> _DecodeGraph:
+    def _decode_graph(self, n_seqs: int, max_pages: int, capture: bool = True, prefer_captured: bool = False) -> _DecodeGraph:
         """The captured step for ``n_seqs`` sequences (padded to a power of two) whose page
         tables hold up to ``max_pages`` pages (padded to 8, 16, 32 ...); captured on first use
         (``capture`` False: only its buffer and batch description are made)."""
@@ -272,6 +272,12 @@ class Engine:
             width *= 2
         key = (n_pad, width)
         g = self._graphs.get(key)
+        if prefer_captured and capture and (g is None or g.graph is None):
+            # A larger captured step of the same page-table width serves as well (more padded
+            # rows) and saves a capture in the middle of a generation that is about to end.
+            have = [k for k, c in self._graphs.items() if k[1] == width and k[0] > n_pad and c.graph is not None]
+            if have:
+                return self._graphs[min(have)]
         if g is None:
             g = self._graphs[key] = _DecodeGraph(n_pad, width)
             g.buffer = torch.zeros(g.layout.size, dtype=torch.int32, device=self.device)

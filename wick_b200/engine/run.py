@@ -90,6 +90,7 @@ class DeviceRun:
         self.pending: Deque[Tuple[int, int]] = collections.deque()
         self.uploads = 0                     # descriptions copied to the device (a test reads it)
         self.h2d_bytes = 0
+        self.left: Dict[int, int] = {}       # tokens each sequence may still be given, as far as the host knows
 
     # ---- the first step: all prompts ----
     def start(self, slots: Sequence[int], prompts: Sequence[Sequence[int]], limits: Sequence[int]) -> None:
@@ -123,8 +124,9 @@ class DeviceRun:
             if self.seen is not None:
                 ops.seen_prompt(self.seen, e.seq_state, batch.slots, batch.tokens, batch.seq_of_token)
             self._sample_and_advance(logits, batch.slots, batch.kv_len, B)
-        for s, q in zip(slots, q_lens):
+        for s, q, lim in zip(slots, q_lens, limits):
             e.cache.advance(s, q)
+            self.left[s] = lim - 1
 
     # ---- one more token each ----
     def launch(self, slots: Sequence[int]) -> None:
@@ -136,7 +138,9 @@ class DeviceRun:
             n = cache.length(s) + 1
             cache.reserve(s, n)
             longest = max(longest, n)
-        g = e._decode_graph(B, (longest + PAGE - 1) // PAGE, capture=e.use_graphs)
+        # (A batch that has shrunk and will end within 64 steps keeps the captured step it has.)
+        ending = max(self.left.get(s, 0) for s in slots) < 64
+        g = e._decode_graph(B, (longest + PAGE - 1) // PAGE, capture=e.use_graphs, prefer_captured=ending)
         composition = (tuple(slots), tuple(len(cache.pages_of(s)) for s in slots))
         if g.composition != composition:
             # (token, position and lengths of the description are written by step_prepare)
@@ -157,6 +161,7 @@ class DeviceRun:
             self._sample_and_advance(logits[:B], b.slots[:B], b.kv_len[:B], B)
         for s in slots:
             cache.advance(s, 1)
+            self.left[s] = self.left.get(s, 1) - 1
 
     def _sample_and_advance(self, logits: torch.Tensor, slots_dev: torch.Tensor, kv_len_dev: torch.Tensor, B: int) -> None:
         e = self.engine
