@@ -50,7 +50,7 @@ __device__ __forceinline__ float rms_scale(float ss, int width, float eps) { ret
 // `rows` the sum is also written back to x.  With `rows` x stays as it is: a row may be
 // named twice, and two blocks that both wrote it back could each read the other's sum.
 template <typename TOut>
-__global__ void rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int splits,
+__global__ void __launch_bounds__(1024) rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int splits,
                                int64_t split_stride, const float* __restrict__ w, float eps,
                                const int* __restrict__ rows, TOut* __restrict__ out, int width) {
     extern __shared__ float smem[];
@@ -359,14 +359,15 @@ int rmsnorm(float* x, const float* delta, int splits, int64_t n_rows_x, const fl
         WICK_CUDA(cudaFuncSetAttribute(rmsnorm_kernel<TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         raised = true;
     }
-    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    const int threads = width >= 4096 ? 1024 : (width >= 2048 ? 512 : (width >= 512 ? 256 : 128));
     if (n_out >= 512 && width % 4 == 0 && width <= 4096) {
         // Enough rows to give every SM its warps: a warp per row (same bits as the block per row).
         // With fewer rows (a decode step of 64 sequences) a warp per row leaves most of the part
         // idle and each warp walks its row's partial sums alone: the block per row is 3x faster there.
         const dim3 grid(ceil_div(n_out, 4)), block(128);
         const int64_t stride = n_rows_x * width;
-        if (threads == 512) WICK_CUDA(launch(rmsnorm_rows_kernel<TOut, 512>, grid, block, 0, s, x, delta, splits, stride, w, eps, rows, (TOut*)out, n_out, width));
+        if (threads == 1024) WICK_CUDA(launch(rmsnorm_rows_kernel<TOut, 1024>, grid, block, 0, s, x, delta, splits, stride, w, eps, rows, (TOut*)out, n_out, width));
+        else if (threads == 512) WICK_CUDA(launch(rmsnorm_rows_kernel<TOut, 512>, grid, block, 0, s, x, delta, splits, stride, w, eps, rows, (TOut*)out, n_out, width));
         else if (threads == 256) WICK_CUDA(launch(rmsnorm_rows_kernel<TOut, 256>, grid, block, 0, s, x, delta, splits, stride, w, eps, rows, (TOut*)out, n_out, width));
         else WICK_CUDA(launch(rmsnorm_rows_kernel<TOut, 128>, grid, block, 0, s, x, delta, splits, stride, w, eps, rows, (TOut*)out, n_out, width));
         return check_launch("rmsnorm");
