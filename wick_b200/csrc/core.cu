@@ -273,6 +273,29 @@ __global__ void qk_norm_rope_append_kernel(
             }
         }
     }
+    // The token's angles and both norm weights are asked for now, with the vectors: one
+    // trip to the memory instead of three in a row.
+    float2 cs[MAXG], sn[MAXG], wq[MAXG][2], wk[MAXG][2];
+    const bool has_k = write_kv && h0 + HB > n_heads;
+#pragma unroll
+    for (int g = 0; g < MAXG; ++g) {
+        const int i = 2 * lane + 64 * g;
+        cs[g] = sn[g] = wq[g][0] = wq[g][1] = wk[g][0] = wk[g][1] = make_float2(0.f, 0.f);
+        if (i < half) {
+            if (cos_t) {
+                cs[g] = *reinterpret_cast<const float2*>(cos_t + (int64_t)t * half + i);
+                sn[g] = *reinterpret_cast<const float2*>(sin_t + (int64_t)t * half + i);
+            }
+            if (q_w && h0 < n_heads) {
+                wq[g][0] = *reinterpret_cast<const float2*>(q_w + i);
+                wq[g][1] = *reinterpret_cast<const float2*>(q_w + i + half);
+            }
+            if (k_w && has_k) {
+                wk[g][0] = *reinterpret_cast<const float2*>(k_w + i);
+                wk[g][1] = *reinterpret_cast<const float2*>(k_w + i + half);
+            }
+        }
+    }
 #pragma unroll
     for (int u = 0; u < HB; ++u) {
         const int h = h0 + u;
@@ -308,16 +331,16 @@ __global__ void qk_norm_rope_append_kernel(
             if (i < half) {
                 float2 a = xa[u][g], b = xb[u][g];
                 if (w) {
-                    a.x = (a.x * scale) * w[i];
-                    a.y = (a.y * scale) * w[i + 1];
-                    b.x = (b.x * scale) * w[i + half];
-                    b.y = (b.y * scale) * w[i + 1 + half];
+                    const float2 wa = h < n_heads ? wq[g][0] : wk[g][0], wb = h < n_heads ? wq[g][1] : wk[g][1];
+                    a.x = (a.x * scale) * wa.x;
+                    a.y = (a.y * scale) * wa.y;
+                    b.x = (b.x * scale) * wb.x;
+                    b.y = (b.y * scale) * wb.y;
                 }
                 if (rotate && cos_t) {
-                    const float2 c = *reinterpret_cast<const float2*>(cos_t + (int64_t)t * half + i);
-                    const float2 sn = *reinterpret_cast<const float2*>(sin_t + (int64_t)t * half + i);
-                    const float rax = a.x * c.x - b.x * sn.x, rbx = b.x * c.x + a.x * sn.x;
-                    const float ray = a.y * c.y - b.y * sn.y, rby = b.y * c.y + a.y * sn.y;
+                    const float2 c = cs[g], s2 = sn[g];
+                    const float rax = a.x * c.x - b.x * s2.x, rbx = b.x * c.x + a.x * s2.x;
+                    const float ray = a.y * c.y - b.y * s2.y, rby = b.y * c.y + a.y * s2.y;
                     a = make_float2(rax, ray);
                     b = make_float2(rbx, rby);
                 }
@@ -326,6 +349,130 @@ __global__ void qk_norm_rope_append_kernel(
             }
         }
     }
+}
+
+// The same for head sizes in steps of 16 with 16-byte aligned arrays: L lanes per vector
+// (L * 8 >= head_dim / 2; a lane holds 8 neighbouring elements and their 8 partners in
+// the rotation), so that a warp takes 32 / L vectors with one stream of instructions.
+// The first form spends ~240 instructions per vector and is bound by their issue (the
+// square root and the divisions of the scale above all, once per vector whatever the
+// number of lanes); this one issues them once per 32 / L vectors.
+__device__ __forceinline__ void load8(const float* p, float* v) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float* v) {
+    const uint4 r = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(h[k]);
+        v[2 * k] = f.x;
+        v[2 * k + 1] = f.y;
+    }
+}
+__device__ __forceinline__ void store8(float* p, const float* v) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float* v) {
+    uint4 r;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) h[k] = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
+    *reinterpret_cast<uint4*>(p) = r;
+}
+
+template <typename T, int L>
+__global__ void __launch_bounds__(128)
+qk_norm_rope_append_vec_kernel(
+    const T* __restrict__ qkv, const float* __restrict__ parts, int splits, int64_t split_stride,
+    int n_tokens, int n_heads, int n_kv, int hd,
+    const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+    const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+    T* __restrict__ q_out, T* __restrict__ kv, const int* __restrict__ page_table, int table_width,
+    const int* __restrict__ seq_of_token, const int* __restrict__ positions, int write_kv) {
+    pdl_trigger();
+    pdl_wait();
+    qkv = fresh(qkv);
+    parts = fresh(parts);
+    cos_t = fresh(cos_t);
+    sin_t = fresh(sin_t);
+    const int heads_total = n_heads + (write_kv ? 2 * n_kv : 0);
+    const int t = blockIdx.x;
+    const int h = (blockIdx.y * blockDim.x + threadIdx.x) / L;      // this group of lanes' vector
+    const int half = hd >> 1;
+    const int i0 = (threadIdx.x % L) * 8;                           // the lane's elements i0 .. i0 + 7 and i0 + half ..
+    const bool live = h < heads_total && i0 < half;                 // (every lane stays for the shuffles)
+    const int row_width = (n_heads + 2 * n_kv) * hd;
+    float a[8], b[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) a[k] = b[k] = 0.f;
+    float c[8], sn[8], wa[8], wb[8];
+    const bool is_q = h < n_heads, is_v = h >= n_heads + n_kv;
+    const float* w = is_q ? q_w : (is_v ? nullptr : k_w);
+    const bool rotate = !is_v && cos_t != nullptr;
+    T* dst = nullptr;
+    if (live) {
+        const int64_t base = (int64_t)t * row_width + (int64_t)h * hd + i0;
+        if (parts) {
+            // float32 partial sums [splits][tokens][row_width], added in index order
+            load8(parts + base, a);
+            load8(parts + base + half, b);
+            for (int sp = 1; sp < splits; ++sp) {
+                float da[8], db[8];
+                load8(parts + sp * split_stride + base, da);
+                load8(parts + sp * split_stride + base + half, db);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    a[k] += da[k];
+                    b[k] += db[k];
+                }
+            }
+        } else {
+            load8(qkv + base, a);
+            load8(qkv + base + half, b);
+        }
+        if (rotate) {
+            load8(cos_t + (int64_t)t * half + i0, c);
+            load8(sin_t + (int64_t)t * half + i0, sn);
+        }
+        if (w) {
+            load8(w + i0, wa);
+            load8(w + i0 + half, wb);
+        }
+        if (is_q) dst = q_out + ((int64_t)t * n_heads + h) * hd + i0;
+        else {
+            const int kh = h - n_heads - (is_v ? n_kv : 0);
+            const int pos = positions[t];
+            const int page = page_table[(int64_t)seq_of_token[t] * table_width + pos / kPage];
+            dst = kv + ((((int64_t)page * 2 + (is_v ? 1 : 0)) * n_kv + kh) * kPage + (pos % kPage)) * hd + i0;
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) ss += a[k] * a[k] + b[k] * b[k];
+#pragma unroll
+    for (int o = L / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (!live) return;
+    if (w) {
+        const float scale = 1.0f / sqrtf(ss / (float)hd + eps);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            a[k] = (a[k] * scale) * wa[k];
+            b[k] = (b[k] * scale) * wb[k];
+        }
+    }
+    if (rotate) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const float ra = a[k] * c[k] - b[k] * sn[k], rb = b[k] * c[k] + a[k] * sn[k];
+            a[k] = ra;
+            b[k] = rb;
+        }
+    }
+    store8(dst, a);
+    store8(dst + half, b);
 }
 
 // ---- SwiGLU on separate arrays ----------------------------------------------
@@ -428,6 +575,21 @@ static int qk_norm_rope_append(const void* qkv, const float* parts, int splits, 
     const int warps = 4;
     const int64_t stride = (int64_t)n_tokens * (n_heads + 2 * n_kv) * hd;
     WICK_REQUIRE(heads_total <= 65535 * warps, "qk_norm_rope_append: %d heads is beyond the grid limit", heads_total);
+    auto aligned = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+    if (hd % 16 == 0 && (stride * (int64_t)sizeof(float)) % 16 == 0 && aligned(qkv) && aligned(parts) && aligned(q_w) && aligned(k_w) &&
+        aligned(cos_t) && aligned(sin_t) && aligned(q_out) && aligned(kv)) {
+        // L lanes of 8 elements (and their partners) per vector
+        const int lanes = hd <= 64 ? 4 : (hd <= 128 ? 8 : 16);
+        const dim3 grid(n_tokens, ceil_div((int64_t)heads_total * lanes, warps * 32)), block(warps * 32);
+#define WICK_QK_VEC(L)                                                                                                         \
+    WICK_CUDA(launch(qk_norm_rope_append_vec_kernel<T, L>, grid, block, 0, s, (const T*)qkv, parts, splits, stride, n_tokens, n_heads, \
+                     n_kv, hd, q_w, k_w, eps, cos_t, sin_t, (T*)q_out, (T*)kv, page_table, table_width, seq_of_token, positions, write_kv))
+        if (lanes == 4) WICK_QK_VEC(4);
+        else if (lanes == 8) WICK_QK_VEC(8);
+        else WICK_QK_VEC(16);
+#undef WICK_QK_VEC
+        return check_launch("qk_norm_rope_append");
+    }
     if ((int64_t)n_tokens * heads_total >= 8192) {            // a prompt: two vectors per warp
         WICK_CUDA(launch(qk_norm_rope_append_kernel<T, 2>, dim3(n_tokens, ceil_div(heads_total, warps * 2)), dim3(warps * 32), 0, s,
                          (const T*)qkv, parts, splits, stride, n_tokens, n_heads, n_kv, hd, q_w, k_w, eps, cos_t, sin_t, (T*)q_out,
