@@ -27,9 +27,13 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
 
 // ---- RMSNorm ---------------------------------------------------------------
 // Two kernels compute it: one block per row (few rows: a decode step) and one warp
-// per row (many rows: a prompt).  They give the same bits: the warp plays every
-// thread of the block in turn, and the operations below are spelled out so that the
-// compiler contracts nothing differently in the two.
+// per row (many rows: a prompt).  They give the same bits.  The sum of squares of a row
+// whose width is a multiple of 4 is defined as: every four neighbouring elements' own sum
+// (sumsq4 from zero); those, 32 apart, added up in index order (class c: quads c, c + 32,
+// ...); the 32 class sums by the butterfly.  A lane of the warp kernel holds exactly one
+// class; the block kernel leaves the quads' sums in shared memory and its first warp adds
+// up the classes.  The operations are spelled out so that the compiler contracts nothing
+// differently in the two.
 __device__ __forceinline__ float sumsq4(float ss, float4 v) {
     return __fadd_rn(ss, __fadd_rn(__fadd_rn(__fadd_rn(__fmul_rn(v.x, v.x), __fmul_rn(v.y, v.y)), __fmul_rn(v.z, v.z)), __fmul_rn(v.w, v.w)));
 }
@@ -50,7 +54,7 @@ __device__ __forceinline__ float rms_scale(float ss, int width, float eps) { ret
 // `rows` the sum is also written back to x.  With `rows` x stays as it is: a row may be
 // named twice, and two blocks that both wrote it back could each read the other's sum.
 template <typename TOut>
-__global__ void __launch_bounds__(1024) rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int splits,
+__global__ void __launch_bounds__(1024, 1) rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ delta, int splits,
                                int64_t split_stride, const float* __restrict__ w, float eps,
                                const int* __restrict__ rows, TOut* __restrict__ out, int width) {
     extern __shared__ float smem[];
@@ -60,6 +64,7 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(float* __restrict__ x, co
     delta = fresh(delta);
     float* row = smem;
     float* red = smem + width;
+    float* quads = red + 40;                            // [width / 4] sums of four neighbouring squares
     const int i = blockIdx.x;
     const int64_t r = rows ? rows[i] : i;
     float* xr = x + r * width;
@@ -76,8 +81,17 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(float* __restrict__ x, co
                 if (!rows) *reinterpret_cast<float4*>(xr + j) = v;      // (selected rows: x stays, see below)
             }
             *reinterpret_cast<float4*>(row + j) = v;
-            ss = sumsq4(ss, v);
+            quads[j >> 2] = sumsq4(0.f, v);
         }
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            float p = 0.f;
+            for (int q = threadIdx.x; q < (width >> 2); q += 32) p = __fadd_rn(p, quads[q]);
+            p = warp_sum(p);
+            if (threadIdx.x == 0) red[0] = p;
+        }
+        __syncthreads();
+        ss = red[0];
     } else {
         for (int j = threadIdx.x; j < width; j += blockDim.x) {
             float v = xr[j];
@@ -88,8 +102,8 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(float* __restrict__ x, co
             row[j] = v;
             ss += v * v;
         }
+        ss = block_sum(ss, red);
     }
-    ss = block_sum(ss, red);
     const float scale = rms_scale(ss, width, eps);
     TOut* o = out + (int64_t)i * width;
     if ((width & 3) == 0) {
@@ -107,10 +121,9 @@ __global__ void __launch_bounds__(1024) rmsnorm_kernel(float* __restrict__ x, co
 }
 
 // One warp per output row, for rows that are a multiple of 4 wide and at most 4096:
-// the row stays in registers, nothing is synchronised but the warp.  VT: the threads the
-// block kernel would run for this width; lane l plays its threads l, l + 32, ... so that
-// the sum of squares is added up in exactly that kernel's order.
-template <typename TOut, int VT>
+// the row stays in registers (lane l holds quads l, l + 32, ...: one class of the sum),
+// nothing is synchronised but the warp.
+template <typename TOut>
 __global__ void __launch_bounds__(128) rmsnorm_rows_kernel(float* __restrict__ x, const float* __restrict__ delta, int splits,
                                                            int64_t split_stride, const float* __restrict__ w, float eps,
                                                            const int* __restrict__ rows, TOut* __restrict__ out, int n_out,
@@ -119,66 +132,50 @@ __global__ void __launch_bounds__(128) rmsnorm_rows_kernel(float* __restrict__ x
     pdl_wait();
     x = fresh(x);
     delta = fresh(delta);
-    constexpr int NW = VT / 32;                         // warps of the block kernel
-    constexpr int KMAX = 4096 / 4 / VT > 0 ? 4096 / 4 / VT : 1;   // float4s per thread of the block kernel (widths up to 4096)
+    constexpr int QMAX = 4096 / 4 / 32;                 // quads of a lane
     const int lane = threadIdx.x & 31;
     const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (i >= n_out) return;
     const int64_t r = rows ? rows[i] : i;
     float* xr = x + r * width;
-    float4 v[NW][KMAX];
+    float4 v[QMAX];
 #pragma unroll
-    for (int wv = 0; wv < NW; ++wv)
-#pragma unroll
-        for (int k = 0; k < KMAX; ++k) {
-            const int j = ((wv * 32 + lane) + k * VT) * 4;
-            v[wv][k] = j < width ? *reinterpret_cast<const float4*>(xr + j) : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
+    for (int m = 0; m < QMAX; ++m) {
+        const int j = (lane + 32 * m) * 4;
+        v[m] = j < width ? *reinterpret_cast<const float4*>(xr + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     if (delta) {
         for (int s = 0; s < splits; ++s) {
 #pragma unroll
-            for (int wv = 0; wv < NW; ++wv)
-#pragma unroll
-                for (int k = 0; k < KMAX; ++k) {
-                    const int j = ((wv * 32 + lane) + k * VT) * 4;
-                    if (j < width) {
-                        const float4 d = *reinterpret_cast<const float4*>(delta + s * split_stride + r * width + j);
-                        v[wv][k].x += d.x; v[wv][k].y += d.y; v[wv][k].z += d.z; v[wv][k].w += d.w;
-                    }
+            for (int m = 0; m < QMAX; ++m) {
+                const int j = (lane + 32 * m) * 4;
+                if (j < width) {
+                    const float4 d = *reinterpret_cast<const float4*>(delta + s * split_stride + r * width + j);
+                    v[m].x += d.x; v[m].y += d.y; v[m].z += d.z; v[m].w += d.w;
                 }
+            }
         }
 #pragma unroll
-        for (int wv = 0; wv < NW; ++wv)
-#pragma unroll
-            for (int k = 0; k < KMAX; ++k) {
-                const int j = ((wv * 32 + lane) + k * VT) * 4;
-                if (j < width && !rows) *reinterpret_cast<float4*>(xr + j) = v[wv][k];
-            }
+        for (int m = 0; m < QMAX; ++m) {
+            const int j = (lane + 32 * m) * 4;
+            if (j < width && !rows) *reinterpret_cast<float4*>(xr + j) = v[m];
+        }
     }
-    // the block kernel's sum: per thread over k, per warp by the butterfly, then over the warps by the butterfly
-    float total_in = 0.f;
+    float p = 0.f;
 #pragma unroll
-    for (int wv = 0; wv < NW; ++wv) {
-        float ss = 0.f;
-#pragma unroll
-        for (int k = 0; k < KMAX; ++k)
-            if (((wv * 32 + lane) + k * VT) * 4 < width) ss = sumsq4(ss, v[wv][k]);
-        ss = warp_sum(ss);
-        if (lane == wv) total_in = ss;
-    }
-    const float scale = rms_scale(warp_sum(total_in), width, eps);
+    for (int m = 0; m < QMAX; ++m)
+        if ((lane + 32 * m) * 4 < width) p = __fadd_rn(p, sumsq4(0.f, v[m]));
+    const float scale = rms_scale(warp_sum(p), width, eps);
     TOut* o = out + (int64_t)i * width;
 #pragma unroll
-    for (int wv = 0; wv < NW; ++wv)
-#pragma unroll
-        for (int k = 0; k < KMAX; ++k) {
-            const int j = ((wv * 32 + lane) + k * VT) * 4;
-            if (j < width) {
-                const float4 g = *reinterpret_cast<const float4*>(w + j);
-                const float4 q = v[wv][k];
-                st4(o + j, normed(q.x, scale, g.x), normed(q.y, scale, g.y), normed(q.z, scale, g.z), normed(q.w, scale, g.w));
-            }
+    for (int m = 0; m < QMAX; ++m) {
+        const int j = (lane + 32 * m) * 4;
+        if (j < width) {
+            const float4 g = *reinterpret_cast<const float4*>(w + j);
+            const float4 q = v[m];
+            st4(o + j, normed(q.x, scale, g.x), normed(q.y, scale, g.y), normed(q.z, scale, g.z), normed(q.w, scale, g.w));
         }
+    }
 }
 
 // x[r] += sum of delta for every row (no norm): resolves a pending residual.
@@ -498,9 +495,9 @@ int rmsnorm(float* x, const float* delta, int splits, int64_t n_rows_x, const fl
             const int* rows, void* out, int n_out, int width, cudaStream_t s) {
     WICK_REQUIRE(width > 0 && n_out >= 0, "rmsnorm: bad sizes");
     if (n_out == 0) return 0;
-    const size_t smem = ((size_t)width + 40) * sizeof(float);
+    const size_t smem = ((size_t)width + 40 + width / 4 + 1) * sizeof(float);
     WICK_REQUIRE(smem <= 200 * 1024, "rmsnorm: width %d is beyond the %d that one block's shared memory holds",
-                 width, 200 * 1024 / 4 - 40);
+                 width, (200 * 1024 / 4 - 41) * 4 / 5);
     static bool raised = false;
     if (smem > 48 * 1024 && !raised) {
         WICK_CUDA(cudaFuncSetAttribute(rmsnorm_kernel<TOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
@@ -513,10 +510,7 @@ int rmsnorm(float* x, const float* delta, int splits, int64_t n_rows_x, const fl
         // idle and each warp walks its row's partial sums alone: the block per row is 3x faster there.
         const dim3 grid(ceil_div(n_out, 4)), block(128);
         const int64_t stride = n_rows_x * width;
-        if (threads == 1024) WICK_CUDA(launch(rmsnorm_rows_kernel<TOut, 1024>, grid, block, 0, s, x, delta, splits, stride, w, eps, rows, (TOut*)out, n_out, width));
-        else if (threads == 512) WICK_CUDA(launch(rmsnorm_rows_kernel<TOut, 512>, grid, block, 0, s, x, delta, splits, stride, w, eps, rows, (TOut*)out, n_out, width));
-        else if (threads == 256) WICK_CUDA(launch(rmsnorm_rows_kernel<TOut, 256>, grid, block, 0, s, x, delta, splits, stride, w, eps, rows, (TOut*)out, n_out, width));
-        else WICK_CUDA(launch(rmsnorm_rows_kernel<TOut, 128>, grid, block, 0, s, x, delta, splits, stride, w, eps, rows, (TOut*)out, n_out, width));
+        WICK_CUDA(launch(rmsnorm_rows_kernel<TOut>, grid, block, 0, s, x, delta, splits, stride, w, eps, rows, (TOut*)out, n_out, width));
         return check_launch("rmsnorm");
     }
     WICK_CUDA(launch(rmsnorm_kernel<TOut>, dim3(n_out), dim3(threads), smem, s, x, delta, splits, n_rows_x * width, w,
