@@ -503,3 +503,77 @@ def test_decoding_beyond_64_pages(dtype, graphs):
     eng = make_engine(name, dtype, max_tokens=8192, use_graphs=graphs)
     poison_all(eng)
     _run_batch_against_plain(name, dtype, eng, (4150, 70), (10, 10), 7000, every=3)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_prompt_steps_replayed_from_captured_steps_of_padded_sizes(dtype):
+    """Prompt steps of up to 512 tokens are replayed from captured steps, padded to a multiple of
+    64 tokens and to a power of two of sequences plus a padding sequence on the reserved page.
+    Steps of different compositions share one captured step; idle sequence entries, the padding
+    tokens and what page 0 holds (NaN here) change no row; a step that is longer, or that
+    continues a sequence beyond 512 positions, is launched kernel by kernel."""
+    name = "D"
+    eng = make_engine(name, dtype, max_tokens=4096)
+    assert eng.prompt_graphs and eng.use_graphs
+    poison_all(eng)
+    V = vocab_of(name)
+
+    def run(lens, seed, whole):
+        seqs = [random_tokens(V, n, seed + i) for i, n in enumerate(lens)]
+        slots = [eng.open_seq() for _ in seqs]
+        want = [list(range(n)) for n in lens] if whole else None
+        got = eng.step(slots, seqs, want)
+        off = 0
+        for i, s in enumerate(seqs):
+            ref = plain_logits(name, s)
+            if whole:
+                assert_logits_close(got[off:off + len(s)], ref, dtype, f"lens {lens} seq {i}")
+                off += len(s)
+            else:
+                assert_logits_close(got[i], ref[-1], dtype, f"lens {lens} seq {i} (last)")
+        return slots, seqs
+
+    def close(slots):
+        for s in slots:
+            eng.close_seq(s)
+        poison_free_pages(eng)
+
+    close(run((30, 41), 300, whole=False)[0])
+    assert set(eng._prompt_graphs) == {(128, 3, 3)}
+    close(run((64, 7), 310, whole=False)[0])                  # the same padded size: the same captured step
+    close(run((1, 127), 320, whole=False)[0])                 # no padding token at all
+    assert set(eng._prompt_graphs) == {(128, 3, 3)}
+    close(run((70,), 330, whole=True)[0])                     # every position wanted: as many rows as tokens
+    assert set(eng._prompt_graphs) == {(128, 3, 3), (128, 2, 128)}
+    close(run((1, 2, 64, 9, 3), 340, whole=True)[0])          # five sequences in eight entries
+    assert (128, 9, 128) in eng._prompt_graphs
+    n_captured = len(eng._prompt_graphs)
+    # a sequence continued beyond 512 positions, and a step of more than 512 tokens: not captured
+    slots, seqs = run((500,), 350, whole=False)
+    more = random_tokens(V, 30, 351)
+    got = eng.step(slots, [more], [list(range(30))])
+    assert_logits_close(got, plain_logits(name, seqs[0] + more)[500:], dtype, "continued beyond 512 positions")
+    close(slots)
+    close(run((300, 290), 360, whole=False)[0])
+    assert len(eng._prompt_graphs) == n_captured + 1          # (the 500-token step)
+    eng.cache.check()
+    assert eng.cache.pages.n_held == 0
+    eng.check_kernels()
+
+
+def test_a_captured_prompt_step_and_the_same_step_launched_give_the_same_logits():
+    """Bits are not promised (the padded size may choose other kernels), closeness is: the
+    same prompts through a captured step and through separate launches."""
+    name = "F"
+    V = vocab_of(name)
+    seqs = [random_tokens(V, n, 400 + n) for n in (90, 3, 33)]
+    out = []
+    for captured in (True, False):
+        eng = make_engine(name, "bfloat16")
+        eng.prompt_graphs = captured
+        slots = [eng.open_seq() for _ in seqs]
+        out.append(eng.step(slots, seqs).float().cpu())
+        assert (len(eng._prompt_graphs) > 0) == captured
+    for i, s in enumerate(seqs):
+        assert_logits_close(out[0][i], plain_logits(name, s)[-1], "bfloat16", f"captured, seq {i}")
+        assert_logits_close(out[1][i], plain_logits(name, s)[-1], "bfloat16", f"launched, seq {i}")

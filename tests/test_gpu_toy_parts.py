@@ -133,6 +133,7 @@ def test_a_mixer_with_its_own_state_is_registered_built_and_stepped(graphs):
     eng = wick.Engine.from_dir(d, dtype="float32", max_tokens=512, use_graphs=graphs)
     kinds = [g.need.kind for g in eng.cache.groups]
     assert sorted(kinds) == ["paged_kv", "state"] and all(len(g.entries) == 2 for g in eng.cache.groups)
+    assert not eng.prompt_graphs            # (the toy mixer walks the host's lists of lengths: its prompt steps are never captured)
     table = eng.model.tensor_table()
     assert "model.layers.1.toy.mix.weight" in table and "model.layers.1.self_attn.q_proj.weight" not in table
     pc, pw = P.read_model_dir(d)

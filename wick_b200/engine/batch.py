@@ -65,7 +65,7 @@ class StepBatch:
 
     def __init__(self, layout: BatchLayout, dev: torch.Tensor, *, q_lens: Sequence[int],
                  starts: Sequence[int], host: Optional[np.ndarray] = None, workspace=None,
-                 kv_bound: Optional[int] = None):
+                 kv_bound: Optional[int] = None, q_tiles: Optional[int] = None):
         L = layout
         self.layout = L
         self.buffer = dev
@@ -82,6 +82,9 @@ class StepBatch:
         # sequence of this step, or more (a captured step is sized for its page table).
         self.workspace = workspace
         self.kv_bound = self.max_kv_len if kv_bound is None else kv_bound
+        # A captured prompt step: the most 64-row work items its sequences can make (the host
+        # lists above then describe no real prompt, see Part.PROMPT_CAPTURABLE); None otherwise.
+        self.q_tiles = q_tiles
         v = lambda off, n: dev[off:off + n]
         self.tokens = v(L.tokens, L.n_tokens)
         self.positions = v(L.positions, L.n_tokens)
@@ -99,8 +102,10 @@ class StepBatch:
 
 def fill_host(layout: BatchLayout, out: np.ndarray, *, tokens: Sequence[Sequence[int]],
               starts: Sequence[int], slots: Sequence[int], pages: Sequence[Sequence[int]],
-              want: Sequence[Sequence[int]], pad_page: int = 0) -> None:
-    """Write every field of the packed buffer ``out`` (int32 [layout.size])."""
+              want: Sequence[Sequence[int]], pad_page: int = 0, pad_want: bool = False) -> None:
+    """Write every field of the packed buffer ``out`` (int32 [layout.size]).  A sequence
+    may bring no token.  pad_want: fewer places may be wanted than the layout holds; the
+    rest name the step's first token."""
     L = layout
     B = L.n_seqs
     out[:] = 0
@@ -125,4 +130,4 @@ def fill_host(layout: BatchLayout, out: np.ndarray, *, tokens: Sequence[Sequence
             w += 1
         t += n
     out[L.cu_seqlens + B] = t
-    assert t == L.n_tokens and w == L.n_want
+    assert t == L.n_tokens and (w == L.n_want or (pad_want and w < L.n_want))

@@ -97,6 +97,25 @@ class _DecodeGraph:
         self.logits: Optional[torch.Tensor] = None
 
 
+PROMPT_GRAPH_TOKENS = 512     # prompt steps of up to this many tokens are captured, padded to a multiple of 64
+PROMPT_GRAPH_SEQS = 64        # ... and of up to this many sequences (padded to a power of two)
+
+
+class _PromptGraph:
+    """A captured prompt step of ``n_tokens`` tokens in ``n_seqs`` sequences, the last of
+    which is padding: it lives in slot 0 and on the reserved page 0 and takes the tokens
+    that fill the step up.  Sequences between the real ones and the padding bring no token."""
+
+    def __init__(self, n_tokens: int, n_seqs: int, n_want: int):
+        self.n_tokens, self.n_seqs, self.n_want = n_tokens, n_seqs, n_want
+        self.table_width = PROMPT_GRAPH_TOKENS // PAGE
+        self.layout = BatchLayout(n_seqs, n_tokens, self.table_width, n_want)
+        self.buffer: Optional[torch.Tensor] = None
+        self.batch: Optional[StepBatch] = None
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+
+
 class Engine:
     def __init__(self, model: Model, *, max_tokens: int, max_seqs: Optional[int] = None,
                  use_graphs: Optional[bool] = None):
@@ -116,6 +135,11 @@ class Engine:
             use_graphs = os.environ.get("WICK_B200_NO_GRAPHS", "") == ""
         self.use_graphs = use_graphs
         self._graphs: Dict[Tuple[int, int], _DecodeGraph] = {}
+        # Short prompt steps are bound by the host's time per launch: they are captured too,
+        # where every part of the model allows it (WICK_B200_NO_PROMPT_GRAPHS=1: never).
+        self.prompt_graphs = (os.environ.get("WICK_B200_NO_PROMPT_GRAPHS", "") == "") and model.prompt_capturable()
+        self._prompt_graphs: Dict[Tuple[int, int, int], _PromptGraph] = {}
+        self._prompt_pool = None
         self._steps_since_check = 0
         # One record per cache slot on the device (length, next token, finished, ...): what a
         # batch that decodes without the host in between is advanced by.  Slot 0 (padding) is
@@ -203,7 +227,9 @@ class Engine:
 
         The result of a captured decode step (one token per sequence, graphs on) is a
         view of that captured step's output buffer: it is valid until the next step of
-        the same batch size runs, so copy it (``.clone()``) to keep it longer."""
+        the same batch size runs, so copy it (``.clone()``) to keep it longer.  (Prompt
+        steps of up to 512 tokens are replayed from captured steps too, padded to a
+        multiple of 64 tokens; their result is copied out before it is returned.)"""
         if want is None:
             want = [[len(t) - 1] for t in tokens]
         self._check(slots, tokens, want)
@@ -216,7 +242,9 @@ class Engine:
         if decode and self.use_graphs:
             logits = self._step_graph(slots, tokens, want, starts)
         else:
-            logits = self._step_eager(slots, tokens, want, starts, q_lens)
+            logits, batch = self._forward_prompt(slots, tokens, want, starts, q_lens)
+            if batch.q_tiles is not None:
+                logits = logits.clone()              # (a captured step's output buffer: the next one overwrites it)
         for s, q in zip(slots, q_lens):
             cache.advance(s, q)
         return logits
@@ -231,8 +259,57 @@ class Engine:
         self._staging.mark(idx)
         return dev, arr
 
-    def _step_eager(self, slots, tokens, want, starts, q_lens) -> torch.Tensor:
-        return self._forward_eager(slots, tokens, want, starts, q_lens)[0]
+    def _forward_prompt(self, slots, tokens, want, starts, q_lens) -> Tuple[torch.Tensor, StepBatch]:
+        """A step of any shape: replayed from a captured step of its padded size where there
+        can be one, else launched kernel by kernel.  Returns the logits of the wanted places
+        and the batch description that ran (a captured step's has padding behind the
+        ``len(slots)`` real sequences)."""
+        g = self._prompt_graph(q_lens, [s + q for s, q in zip(starts, q_lens)], sum(len(w) for w in want))
+        if g is None:
+            return self._forward_eager(slots, tokens, want, starts, q_lens)
+        B, cache = len(slots), self.cache
+        idle = g.n_seqs - 1 - B
+        fill = g.n_tokens - sum(q_lens)
+        pages = [cache.pages_of(s)[:(st + q + PAGE - 1) // PAGE] for s, st, q in zip(slots, starts, q_lens)]
+        self._upload(g.layout, g.buffer, tokens=[list(t) for t in tokens] + [[]] * idle + [[0] * fill],
+                     starts=list(starts) + [0] * (idle + 1), slots=list(slots) + [0] * (idle + 1),
+                     pages=pages + [[0]] * (idle + 1), want=[list(w) for w in want] + [[]] * (idle + 1), pad_want=True)
+        g.graph.replay()
+        ops.launches[0] += g.kernels
+        self._count_step()
+        return g.logits[:sum(len(w) for w in want)], g.batch
+
+    def _prompt_graph(self, q_lens, kv_lens, n_want: int) -> Optional[_PromptGraph]:
+        """The captured step that serves a prompt step of these lengths (captured on first
+        use), or None: graphs are off, a part of the model does not allow it, or the step is
+        larger than what is captured."""
+        if not (self.use_graphs and self.prompt_graphs):
+            return None
+        n_tokens, B = sum(q_lens), len(q_lens)
+        if n_tokens > PROMPT_GRAPH_TOKENS or B > PROMPT_GRAPH_SEQS or max(kv_lens) > PROMPT_GRAPH_TOKENS:
+            return None
+        t_pad = (n_tokens + PAGE - 1) // PAGE * PAGE
+        n_seqs = self._bucket(B) + 1
+        if n_want > t_pad:
+            return None
+        w_pad = n_seqs if n_want <= n_seqs else t_pad
+        key = (t_pad, n_seqs, w_pad)
+        g = self._prompt_graphs.get(key)
+        if g is None:
+            g = _PromptGraph(t_pad, n_seqs, w_pad)
+            g.buffer = torch.zeros(g.layout.size, dtype=torch.int32, device=self.device)
+            # (host lists: all tokens in one sequence, which is what the capture below runs)
+            g.batch = StepBatch(g.layout, g.buffer, q_lens=[0] * (n_seqs - 1) + [t_pad], starts=[0] * n_seqs,
+                                workspace=self.workspace, q_tiles=t_pad // ops.Q_TILE + n_seqs)
+            # Captured on padding only: every token in the padding sequence, whose page table
+            # names the reserved page 0 throughout, so that no live sequence is touched.
+            self._upload(g.layout, g.buffer, tokens=[[]] * (n_seqs - 1) + [[0] * t_pad], starts=[0] * n_seqs,
+                         slots=[0] * n_seqs, pages=[[0]] * n_seqs, want=[[]] * n_seqs, pad_want=True)
+            if self._prompt_pool is None:
+                self._prompt_pool = torch.cuda.graph_pool_handle()
+            self._capture(g, pool=self._prompt_pool)
+            self._prompt_graphs[key] = g
+        return g
 
     def _forward_eager(self, slots, tokens, want, starts, q_lens) -> Tuple[torch.Tensor, StepBatch]:
         cache = self.cache
@@ -315,7 +392,7 @@ class Engine:
             return g.logits[:0]
         return g.logits[torch.tensor(rows, device=self.device)]
 
-    def _capture(self, g: _DecodeGraph) -> None:
+    def _capture(self, g, pool=None) -> None:
         def run():
             g.batch.memo.clear()
             with ops.stream_scope():                # (entered on the stream that runs or captures the step)
@@ -332,7 +409,7 @@ class Engine:
         self.workspace.frozen = True
         before = ops.launches[0]
         try:
-            with torch.cuda.graph(graph):
+            with torch.cuda.graph(graph, pool=pool):     # (prompt steps share one pool: they never run at the same time)
                 g.logits = run()
         finally:
             self.workspace.frozen = False

@@ -118,12 +118,12 @@ class DeviceRun:
         for s, st, p in zip(slots, starts, prompts):
             e.cache.reserve(s, st + len(p))
         q_lens = [len(p) for p in prompts]
-        logits, batch = e._forward_eager(list(slots), prompts, [[q - 1] for q in q_lens], starts, q_lens)
+        logits, batch = e._forward_prompt(list(slots), [list(p) for p in prompts], [[q - 1] for q in q_lens], starts, q_lens)
         self.h2d_bytes += batch.layout.size * 4
         with ops.stream_scope():
-            if self.seen is not None:
+            if self.seen is not None:                    # (a captured step's padding tokens belong to slot 0: not marked)
                 ops.seen_prompt(self.seen, e.seq_state, batch.slots, batch.tokens, batch.seq_of_token)
-            self._sample_and_advance(logits, batch.slots, batch.kv_len, B)
+            self._sample_and_advance(logits[:B], batch.slots[:B], batch.kv_len[:B], B)
         for s, q, lim in zip(slots, q_lens, limits):
             e.cache.advance(s, q)
             self.left[s] = lim - 1

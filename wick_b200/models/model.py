@@ -109,6 +109,14 @@ class Model:
             n += b.mixer.weight_bytes() + b.ffn.weight_bytes() + b.mixer_norm.weight_bytes() + b.ffn_norm.weight_bytes()
         return n
 
+    def prompt_capturable(self) -> bool:
+        """Whether every part reads a prompt step's shape from the device only, so that a
+        captured prompt step can be replayed for other prompts of the same padded size."""
+        parts: List[Part] = [self.embedding, self.final_norm, self.head]
+        for b in self.blocks:
+            parts += [b, b.mixer, b.mixer_norm, b.ffn, b.ffn_norm]
+        return all(p.PROMPT_CAPTURABLE for p in parts)
+
     # ---- forward -------------------------------------------------------------
     def forward(self, batch, cache) -> torch.Tensor:
         """Run the batch's tokens through every scheduled layer, appending to the

@@ -326,6 +326,8 @@ def attention_tiles(batch) -> int:
     """How many work items the prompt attention kernels cut this step into: one per 64 new
     tokens of a sequence, numbered sequence by sequence (a kernel finds its item's sequence
     and first row from the step's ``cu_seqlens``)."""
+    if getattr(batch, "q_tiles", None) is not None:
+        return batch.q_tiles                 # (a captured step: the most there can be; a kernel skips items beyond the last)
     return sum((q + Q_TILE - 1) // Q_TILE for q in batch.q_lens)
 
 

@@ -89,6 +89,13 @@ class Part:
     # "head"): the model hands them over through :meth:`attach` before any weight is loaded.
     # (An output head that shares the embedding table names "embedding".)
     PEERS: Tuple[str, ...] = ()
+    # True if a prompt step of this part reads the step's shape (which token belongs to which
+    # sequence, lengths, positions, pages) from the batch's DEVICE arrays only and sizes its
+    # launches by ``batch.n_tokens``, ``batch.n_seqs`` and ``batch.q_tiles`` alone.  The engine
+    # captures prompt steps of padded sizes and replays them for other prompts only if every
+    # part of the model says so; the host lists of such a captured batch (``q_lens``,
+    # ``starts``) describe no real prompt.
+    PROMPT_CAPTURABLE = False
 
     def __init__(self, params: Mapping[str, Any], ctx: BuildContext):
         self.params = dict(params)

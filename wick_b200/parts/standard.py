@@ -38,6 +38,8 @@ from .linear import Linear
 
 # ---------------------------------------------------------------------------
 class RMSNorm(Norm):
+    PROMPT_CAPTURABLE = True
+
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
         self.width = int(params["width"])
@@ -69,6 +71,8 @@ class RotaryHalfSplit(Position):
     ``position * inv_freq[i]`` with ``inv_freq[i] = theta ** (-2i / head_dim)``,
     evaluated in float64 and rounded to float32 once."""
 
+    PROMPT_CAPTURABLE = True
+
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
         self.head_dim = int(params["head_dim"])
@@ -91,6 +95,8 @@ class RotaryHalfSplit(Position):
 
 
 class NoPosition(Position):
+    PROMPT_CAPTURABLE = True
+
     def rotary_inv_freq(self):
         return None
 
@@ -129,6 +135,7 @@ class GQAttention(Mixer):
         if qk is not None and not isinstance(self.q_norm, RMSNorm):
             raise ValueError("the fused q/k norm kernel is an RMS norm; another norm needs its own kernel")
         self.position = build_part("position", p.get("position") or PartSpec("none"), ctx)
+        self.PROMPT_CAPTURABLE = bool(self.position.PROMPT_CAPTURABLE)   # (its own kernels read the step from the device)
         self.qkv = Linear(self.q_dim + 2 * self.kv_dim, self.width, ctx)
         self.o = Linear(self.width, self.q_dim, ctx)
 
@@ -235,6 +242,8 @@ class GQAttention(Mixer):
 class GatedMLP(FeedForward):
     """down( act(x gate^T) * (x up^T) ), no biases; gate and up are one matrix."""
 
+    PROMPT_CAPTURABLE = True
+
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
         self.width, self.intermediate = int(params["width"]), int(params["intermediate"])
@@ -278,6 +287,8 @@ class PreNormResidual(Block):
     part whose class says ``ADDS_TO_RESIDUAL`` is handed the residual stream and
     returns None when it has added its result to it (its last kernel did)."""
 
+    PROMPT_CAPTURABLE = True
+
     def forward(self, h, batch, cache, write_cache):
         dt = self.ctx.dtype
         if h.pending is not None:
@@ -299,6 +310,8 @@ class PreNormResidual(Block):
 
 # ---------------------------------------------------------------------------
 class TableEmbedding(Embedding):
+    PROMPT_CAPTURABLE = True
+
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
         self.vocab, self.width = int(params["vocab"]), int(params["width"])
@@ -323,6 +336,8 @@ class TableEmbedding(Embedding):
 class LinearHead(Head):
     """logits = x W^T in float32.  ``tied``: W is the embedding table.  As in wick
     (model.rs:190) the head is also tied when its own tensor is absent."""
+
+    PROMPT_CAPTURABLE = True
 
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
