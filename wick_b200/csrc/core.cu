@@ -13,15 +13,51 @@
 namespace wick {
 
 
+// Eight neighbouring elements at a 16-byte aligned place, as float32.
+__device__ __forceinline__ void load8(const float* p, float* v) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float* v) {
+    const uint4 r = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(h[k]);
+        v[2 * k] = f.x;
+        v[2 * k + 1] = f.y;
+    }
+}
+__device__ __forceinline__ void store8(float* p, const float* v) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float* v) {
+    uint4 r;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) h[k] = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
+    *reinterpret_cast<uint4*>(p) = r;
+}
+
 // ---- embedding -------------------------------------------------------------
+// vec: the width is a multiple of 8 and the table is 16-byte aligned (eight elements a load).
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens,
-                             float* __restrict__ out, int width) {
+                             float* __restrict__ out, int width, int vec) {
     pdl_trigger();
     pdl_wait();
     const int64_t row = blockIdx.x;
     const T* src = table + (int64_t)tokens[row] * width;
     float* dst = out + row * width;
+    if (vec) {
+        for (int j = threadIdx.x * 8; j < width; j += blockDim.x * 8) {
+            float v[8];
+            load8(src + j, v);
+            store8(dst + j, v);
+        }
+        return;
+    }
     for (int j = threadIdx.x; j < width; j += blockDim.x) dst[j] = ld(src + j);
 }
 
@@ -354,32 +390,6 @@ __global__ void qk_norm_rope_append_kernel(
 // The first form spends ~240 instructions per vector and is bound by their issue (the
 // square root and the divisions of the scale above all, once per vector whatever the
 // number of lanes); this one issues them once per 32 / L vectors.
-__device__ __forceinline__ void load8(const float* p, float* v) {
-    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-}
-__device__ __forceinline__ void load8(const __nv_bfloat16* p, float* v) {
-    const uint4 r = *reinterpret_cast<const uint4*>(p);
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-        const float2 f = __bfloat1622float2(h[k]);
-        v[2 * k] = f.x;
-        v[2 * k + 1] = f.y;
-    }
-}
-__device__ __forceinline__ void store8(float* p, const float* v) {
-    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
-    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
-}
-__device__ __forceinline__ void store8(__nv_bfloat16* p, const float* v) {
-    uint4 r;
-    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
-#pragma unroll
-    for (int k = 0; k < 4; ++k) h[k] = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
-    *reinterpret_cast<uint4*>(p) = r;
-}
-
 template <typename T, int L>
 __global__ void __launch_bounds__(128)
 qk_norm_rope_append_vec_kernel(
@@ -486,7 +496,8 @@ template <typename T>
 int embed(const void* table, const int* tokens, float* out, int n, int width, int64_t vocab, cudaStream_t s) {
     WICK_REQUIRE(n >= 0 && width > 0 && vocab > 0, "embed: bad sizes n=%d width=%d", n, width);
     if (n == 0) return 0;
-    WICK_CUDA(launch(embed_kernel<T>, dim3(n), dim3(256), 0, s, (const T*)table, tokens, out, width));
+    const int vec = width % 8 == 0 && ((uintptr_t)table & 15) == 0 && ((uintptr_t)out & 15) == 0;
+    WICK_CUDA(launch(embed_kernel<T>, dim3(n), dim3(256), 0, s, (const T*)table, tokens, out, width, vec));
     return check_launch("embed");
 }
 
