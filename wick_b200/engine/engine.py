@@ -99,6 +99,7 @@ class _DecodeGraph:
 
 PROMPT_GRAPH_TOKENS = 512     # prompt steps of up to this many tokens are captured, padded to a multiple of 64
 PROMPT_GRAPH_SEQS = 64        # ... and of up to this many sequences (padded to a power of two)
+PROMPT_GRAPH_COUNT = 24       # captured prompt steps an engine keeps (each holds its output rows); further shapes are launched
 
 
 class _PromptGraph:
@@ -295,6 +296,8 @@ class Engine:
         w_pad = n_seqs if n_want <= n_seqs else t_pad
         key = (t_pad, n_seqs, w_pad)
         g = self._prompt_graphs.get(key)
+        if g is None and len(self._prompt_graphs) >= PROMPT_GRAPH_COUNT:
+            return None
         if g is None:
             g = _PromptGraph(t_pad, n_seqs, w_pad)
             g.buffer = torch.zeros(g.layout.size, dtype=torch.int32, device=self.device)
