@@ -329,7 +329,7 @@ def test_decode_batch_beyond_148_pairs_at_real_widths(dtype, graphs):
     """22 sequences of 1 to 700 tokens at the real widths (config R: 8 kv heads, so 176
     (sequence, kv head) pairs): the prompts in one step, then up to 9 decoded tokens each,
     the shorter requests leaving earlier, so that the batch runs at 22, 19, 17 ... sequences
-    (batch buckets 32 and 16) and the decode attention for many pairs runs inside the engine."""
+    (captured steps of 24 and 16 rows) and the decode attention for many pairs runs inside the engine."""
     name = "R"
     lens = (1, 700, 3, 64, 65, 127, 128, 129, 130, 2, 255, 256, 257, 31, 300, 20, 5, 385, 77, 200, 192, 193)
     n_decode = tuple(9 - (i % 4) * 2 if i % 5 else 9 for i in range(len(lens)))

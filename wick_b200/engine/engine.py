@@ -98,7 +98,7 @@ class _DecodeGraph:
 
 
 PROMPT_GRAPH_TOKENS = 512     # prompt steps of up to this many tokens are captured, padded to a multiple of 64
-PROMPT_GRAPH_SEQS = 64        # ... and of up to this many sequences (padded to a power of two)
+PROMPT_GRAPH_SEQS = 64        # ... and of up to this many sequences (padded to a power of two or three quarters of one)
 PROMPT_GRAPH_COUNT = 24       # captured prompt steps an engine keeps (each holds its output rows); further shapes are launched
 
 
@@ -337,13 +337,16 @@ class Engine:
     # ---- captured decode -------------------------------------------------------
     @staticmethod
     def _bucket(n: int) -> int:
+        """The padded size of a batch of ``n``: a power of two, or (from 24 on) three quarters of
+        one: 1, 2, 4, 8, 16, 24, 32, 48, 64, 96, ...  (A batch of 40 pays for 48 rows in the matrix
+        products and for 48 sequences' pairs in the attention, not for 64.)"""
         b = 1
         while b < n:
             b *= 2
-        return b
+        return b // 4 * 3 if b >= 32 and n <= b // 4 * 3 else b
 
     def _decode_graph(self, n_seqs: int, max_pages: int, capture: bool = True, prefer_captured: bool = False) -> _DecodeGraph:
-        """The captured step for ``n_seqs`` sequences (padded to a power of two) whose page
+        """The captured step for ``n_seqs`` sequences (padded, see :meth:`_bucket`) whose page
         tables hold up to ``max_pages`` pages (padded to 8, 16, 32 ...); captured on first use
         (``capture`` False: only its buffer and batch description are made)."""
         n_pad = self._bucket(n_seqs)
