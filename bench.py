@@ -13,7 +13,7 @@ decode step of the whole batch.
 exactly K steps after W warm-up steps, as the median of three such regions
 (``spread`` has the fastest and the slowest); ``e2e``: the same through the Python
 entry point ``wick_b200.generate``, token ids going in and coming out on the host.
-``prefill``: one 2,048-token prompt (median of three).  ``roofline``: the bytes a
+``prefill``: one 2,048-token prompt (median of 40 steps back to back, about a second).  ``roofline``: the bytes a
 decode step has to read (every weight it uses once, plus the cache of the live
 requests) over its time, against the measured copy bandwidth.  ``points``: decode
 at batch 1 and 64, and the workloads at Qwen3-14B sizes (ragged batch of 16,
@@ -317,7 +317,12 @@ def main() -> int:
     # ---- prefill of one 2,048-token prompt ----
     ptoks = random_prompts(torch, vocab, [n_prefill], 3)[0]
     times = []
-    for i in range(0 if args.skip_prefill else 2 + 3):
+    # The fraction is of the peak SUSTAINED under the power cap (a seconds-long loop of products), so the prompt
+    # step is timed in the same state: after 3 warm-up steps, a second or so of steps back to back (the first
+    # steps of a product-heavy phase run at the part's full clock, the next ones while the power control settles).
+    pf_warm = 3
+    pf_timed = 0 if args.skip_prefill else max(5, min(40, int(40 * 2048 / max(n_prefill, 1))))
+    for i in range(0 if args.skip_prefill else pf_warm + pf_timed):
         s = eng.open_seq()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -326,7 +331,7 @@ def main() -> int:
         e1.record()
         torch.cuda.synchronize()
         eng.close_seq(s)
-        if i >= 2:
+        if i >= pf_warm:
             times.append(e0.elapsed_time(e1))
             head["finite"] = head["finite"] and bool(torch.isfinite(plog).all().item())
     pms = statistics.median(times) if times else float("nan")
@@ -337,7 +342,7 @@ def main() -> int:
     prefill = {"value": n_prefill / (pms * 1e-3), "tokens": n_prefill, "ms": pms,
                "frac": flops / (pms * 1e-3) / 1e12 / pk["bf16_tflops_sustained"],
                "tflops": flops / (pms * 1e-3) / 1e12, "peak_tflops": pk["bf16_tflops_sustained"],
-               "ms_min": min(times) if times else None, "ms_max": max(times) if times else None}
+               "ms_min": min(times) if times else None, "ms_max": max(times) if times else None, "timed_steps": len(times)}
 
     # ---- other batch sizes, other models ----
     points = {}
