@@ -577,3 +577,25 @@ def test_a_captured_prompt_step_and_the_same_step_launched_give_the_same_logits(
     for i, s in enumerate(seqs):
         assert_logits_close(out[0][i], plain_logits(name, s)[-1], "bfloat16", f"captured, seq {i}")
         assert_logits_close(out[1][i], plain_logits(name, s)[-1], "bfloat16", f"launched, seq {i}")
+
+
+def test_the_plain_kernels_switch_runs_the_bfloat16_model_without_tensor_cores(monkeypatch):
+    """WICK_B200_PLAIN=1: every matrix product and attention of the bfloat16 model through the
+    plain CUDA-core twins; no tensor-core kernel is called, and the logits hold against the
+    plain implementation like the fast kernels' do."""
+    from wick_b200 import ops
+    from wick_b200.ops import gemm_tc
+
+    def never(*a, **k):
+        raise AssertionError("a tensor-core kernel ran under the plain-kernels switch")
+
+    monkeypatch.setattr(ops, "PLAIN_KERNELS", True)
+    monkeypatch.setattr(gemm_tc, "gemm_tc", never)
+    monkeypatch.setattr(gemm_tc, "gemm_tc_pair", never)
+    monkeypatch.setattr(ops, "attention_decode_parts_fused", never)
+    monkeypatch.setattr(ops, "attention_decode_parts", never)
+    name = "D"
+    eng = make_engine(name, "bfloat16")
+    poison_all(eng)
+    assert ops.attention_prompt_kind(64, torch.bfloat16) == "plain" and ops.attention_decode_kind(64, torch.bfloat16) == "plain"
+    _run_batch_against_plain(name, "bfloat16", eng, (70, 5, 130), (6, 3, 6), 9000)

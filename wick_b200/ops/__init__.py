@@ -75,6 +75,16 @@ _libs: Dict[str, _Lib] = {}
 # at capture; the engine adds them again at every replay).
 launches = [0]
 
+# WICK_B200_PLAIN=1 (or PLAIN_KERNELS = True): every matrix product and every attention runs
+# through its plain CUDA-core twin (float32 accumulation, no tensor cores, no bulk copies),
+# whatever the compute dtype: the slow form that the fast kernels are held against, for
+# telling a kernel's fault from a model's.
+PLAIN_KERNELS = os.environ.get("WICK_B200_PLAIN", "") not in ("", "0")
+
+
+def plain_kernels() -> bool:
+    return PLAIN_KERNELS
+
 
 CORE_SOURCES = ["core.cu", "sample.cu", "state.cu"]
 
@@ -335,7 +345,7 @@ def attention_prompt_kind(head_dim: int, dtype: torch.dtype, plain: bool = False
     """Which prompt kernel runs: ``tc`` (tcgen05: bfloat16, head sizes 64 and 128),
     ``mma`` (mma.sync: bfloat16, other head sizes up to 128) or ``plain`` (CUDA
     cores: float32, larger heads, and the twin the others are checked against)."""
-    if plain or dtype != torch.bfloat16 or head_dim > 128:
+    if plain or PLAIN_KERNELS or dtype != torch.bfloat16 or head_dim > 128:
         return "plain"
     return "tc" if head_dim in (64, 128) else "mma"
 
@@ -377,7 +387,7 @@ def attention_decode_kind(head_dim: int, dtype: torch.dtype, plain: bool = False
     """Which of the CUDA-core decode kernels :func:`attention_decode` runs: ``fast`` (from
     bulk-copied page tiles) or ``plain``.  (The tensor-core decode attention, bfloat16 at head
     sizes 64 and 128, is :func:`attention_decode_parts`.)"""
-    return "plain" if plain else "fast"
+    return "plain" if plain or PLAIN_KERNELS else "fast"
 
 
 def attention_decode_split(head_dim: int, dtype: torch.dtype, plain: bool = False) -> int:

@@ -53,7 +53,7 @@ class Linear:
         """The tensor-core plan of this matrix, or None where it does not apply."""
         if self._tc is None:
             from ..ops import gemm_tc
-            self._tc = gemm_tc.plan_for(self.weight, gated=self.gated) or False
+            self._tc = (not ops.plain_kernels() and gemm_tc.plan_for(self.weight, gated=self.gated)) or False
         return self._tc or None
 
     def forward(self, x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:

@@ -185,7 +185,7 @@ class GQAttention(Mixer):
             cos = sin = None
             if inv_freq is not None:
                 cos, sin = self.position.tables(batch)
-            if batch.is_decode and qkv.shape[0] <= 8 and ops.attention_decode_parts_supported(
+            if batch.is_decode and qkv.shape[0] <= 8 and not ops.plain_kernels() and ops.attention_decode_parts_supported(
                     batch.n_seqs, self.heads, self.kv_heads, self.head_dim, self.ctx.dtype):
                 # the tensor-core decode attention: the projection's sums, the q/k norm, the rotation,
                 # the cache append, the attention and the merge in one or two launches
