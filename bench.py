@@ -165,8 +165,7 @@ def device_timed_decode(torch, wick, eng, prompts, steps, warmup, repeats=REPEAT
         torch.cuda.synchronize()
         regions.append(e0.elapsed_time(e1) / steps)
         launches = ops.launches[0] - l0
-    g = next(iter(eng._graphs.values()))
-    finite = bool(torch.isfinite(g.logits[:1]).all().item()) if g.logits is not None else False
+    finite = run.last_logits is not None and bool(torch.isfinite(run.last_logits).all().item())
     eng.check_kernels()
     for s in slots:
         eng.close_seq(s)

@@ -91,6 +91,7 @@ class DeviceRun:
         self.uploads = 0                     # descriptions copied to the device (a test reads it)
         self.h2d_bytes = 0
         self.left: Dict[int, int] = {}       # tokens each sequence may still be given, as far as the host knows
+        self.last_logits: Optional[torch.Tensor] = None   # the last step's rows (a view: the next step overwrites them)
 
     # ---- the first step: all prompts ----
     def start(self, slots: Sequence[int], prompts: Sequence[Sequence[int]], limits: Sequence[int]) -> None:
@@ -124,6 +125,7 @@ class DeviceRun:
             if self.seen is not None:                    # (a captured step's padding tokens belong to slot 0: not marked)
                 ops.seen_prompt(self.seen, e.seq_state, batch.slots, batch.tokens, batch.seq_of_token)
             self._sample_and_advance(logits[:B], batch.slots[:B], batch.kv_len[:B], B)
+        self.last_logits = logits[:B]
         for s, q, lim in zip(slots, q_lens, limits):
             e.cache.advance(s, q)
             self.left[s] = lim - 1
@@ -159,6 +161,7 @@ class DeviceRun:
                 b.memo.clear()
                 logits = e.model.forward(b, cache)
             self._sample_and_advance(logits[:B], b.slots[:B], b.kv_len[:B], B)
+        self.last_logits = logits[:B]
         for s in slots:
             cache.advance(s, 1)
             self.left[s] = self.left.get(s, 1) - 1
