@@ -256,25 +256,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
             tc_fence_after();
             if (GATED == 3) {
-                // Lanes 0-63 of the accumulator hold gate rows, lanes 64-127 the up rows of
-                // the same outputs.  Warps 2 and 3 pass their values through shared memory
-                // to warps 0 and 1, which finish and store (transposed output only).
-                const int mg = m0 + (q & 1) * 32 + lane;
+                // Lanes 0-63 of the accumulator hold gate rows, lanes 64-127 the up rows of the
+                // same outputs (transposed output only).  Of every 16 columns the warps of the gate
+                // rows finish and store the first 8, the warps of the up rows the last 8 (the
+                // activation's exponential and division are the long part of a decode block's
+                // end: all four warps share them); what each side lacks crosses through shared
+                // memory.
+                const int mg = m0 + (q & 1) * 32 + lane, xrow = (q & 1) * 32 + lane;
+                const bool upper = q >= 2;
                 for (int c0 = 0; c0 < p.bn; c0 += 16) {
                     float v[16];
                     if (ok && n_kb > 0) tc_ld16(lane_addr + c0, v);
                     float (*xb)[17] = xch[(c0 >> 4) & 1];
-                    if (q >= 2) {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) xb[(q - 2) * 32 + lane][j] = v[j];
-                    }
+                    for (int j = 0; j < 8; ++j) xb[xrow][upper ? j : 8 + j] = upper ? v[j] : v[8 + j];
                     asm volatile("bar.sync 1, 128;" ::: "memory");
-                    if (q < 2 && ok && n_kb > 0 && mg < p.a_rows) {
+                    if (ok && n_kb > 0 && mg < p.a_rows) {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j) {
+                        for (int jj = 0; jj < 8; ++jj) {
+                            const int j = upper ? 8 + jj : jj;
                             const int n = n0 + c0 + j;
                             if (n < p.b_rows) {
-                                const float g = v[j], u = xb[q * 32 + lane][j];
+                                const float mine = upper ? v[8 + jj] : v[jj], other = xb[xrow][j];
+                                const float g = upper ? other : mine, u = upper ? mine : other;
                                 const float r = g / (1.0f + expf(-g)) * u;
                                 const long long off = (long long)n * p.ldo + mg;
                                 if (OUT_F32) ((float*)out_base)[off] = r;
