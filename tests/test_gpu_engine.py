@@ -599,3 +599,61 @@ def test_the_plain_kernels_switch_runs_the_bfloat16_model_without_tensor_cores(m
     poison_all(eng)
     assert ops.attention_prompt_kind(64, torch.bfloat16) == "plain" and ops.attention_decode_kind(64, torch.bfloat16) == "plain"
     _run_batch_against_plain(name, "bfloat16", eng, (70, 5, 130), (6, 3, 6), 9000)
+
+
+@pytest.mark.parametrize("seed", [21, 22])
+def test_random_configurations_prompt_decode_and_chunked_prompt(seed):
+    """Configurations drawn at random (head sizes, groups, widths and vocabularies that are no
+    power of two, tied and untied heads): unequal prompts in one step, decoding, then the same
+    prompts in two chunks on reused slots, in float32 and bfloat16 against the plain implementation."""
+    import random
+
+    import helpers as H
+    rnd = random.Random(seed)
+    for ci in range(3):
+        hd = rnd.choice([16, 32, 64, 128])
+        kv = rnd.choice([1, 2, 3])
+        heads = kv * rnd.choice([1, 2, 3, 5, 8])
+        vocab = rnd.choice([257, 1003, 5003])
+        cfgj = dict(architectures=["Qwen3ForCausalLM"], hidden_size=rnd.choice([72, 200, 320, 520]), num_attention_heads=heads,
+                    num_key_value_heads=kv, head_dim=hd, intermediate_size=rnd.choice([88, 160, 1000]),
+                    num_hidden_layers=rnd.choice([1, 2, 3]), vocab_size=vocab, max_position_embeddings=1024,
+                    rope_theta=rnd.choice([10000.0, 1000000.0]), rms_norm_eps=rnd.choice([1e-6, 1e-5]),
+                    tie_word_embeddings=rnd.random() < 0.5)
+        name = f"random-{seed}-{ci}"
+        H.CONFIGS[name] = cfgj
+        lens = [rnd.choice([1, 2, 5, 63, 64, 65, 129, 200, 257]) for _ in range(rnd.choice([1, 3, 5]))]
+        n_dec = rnd.choice([3, 20])
+        seqs = [random_tokens(vocab, n + n_dec, 100 * ci + i) for i, n in enumerate(lens)]
+        refs = [plain_logits(name, s) for s in seqs]
+        for dtype in DTYPES:
+            what = f"{cfgj} lens {lens} {dtype}"
+            eng = make_engine(name, dtype, max_tokens=4096)
+            poison_all(eng)
+            slots = [eng.open_seq() for _ in seqs]
+            got = eng.step(slots, [s[:n] for s, n in zip(seqs, lens)], [list(range(n)) for n in lens]).clone()
+            off = 0
+            for i, n in enumerate(lens):
+                assert_logits_close(got[off:off + n], refs[i][:n], dtype, f"prompt {i} of {what}")
+                off += n
+            for k in range(n_dec):
+                got = eng.step(slots, [[s[n + k]] for s, n in zip(seqs, lens)]).clone()
+                for i, n in enumerate(lens):
+                    assert_logits_close(got[i], refs[i][n + k], dtype, f"seq {i} decode {k} of {what}")
+            for s in slots:
+                eng.close_seq(s)
+            poison_free_pages(eng)
+            slots = [eng.open_seq() for _ in seqs]
+            cut = [max(1, n // 2) for n in lens]
+            eng.step(slots, [s[:c] for s, c in zip(seqs, cut)], [[] for _ in lens])
+            live = [i for i, n in enumerate(lens) if n > cut[i]]
+            if live:
+                got = eng.step([slots[i] for i in live], [seqs[i][cut[i]:lens[i]] for i in live],
+                               [[lens[i] - cut[i] - 1] for i in live]).clone()
+                for j, i in enumerate(live):
+                    assert_logits_close(got[j], refs[i][lens[i] - 1], dtype, f"chunked prompt {i} of {what}")
+            for s in slots:
+                eng.close_seq(s)
+            eng.cache.check()
+            eng.check_kernels()
+            del eng
