@@ -136,6 +136,32 @@ __device__ __forceinline__ float ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// The softmax warps are bound by the number of instructions they issue: two products-and-sums,
+// two sums, or a maximum of three per instruction where sm_100 has one.
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {      // a * b + c, each half rounded once
+    uint64_t ra, rb, rc, rd;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rc) : "f"(c.x), "f"(c.y));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
+    float2 d;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+    return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    uint64_t ra, rb, rd;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
+    float2 d;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+    return d;
+}
 
 // Descriptors.  A k-major operand (Q, K): rows of 128 bytes, eight-row groups 1024
 // bytes apart, the leading offset unused (1).  The MN-major operand (V): rows are
@@ -304,11 +330,11 @@ attn_prompt_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_co
             }
             float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int i = 0; i < HALF_K; i += 4) {
-                mx4[0] = fmaxf(mx4[0], s[i]);
-                mx4[1] = fmaxf(mx4[1], s[i + 1]);
-                mx4[2] = fmaxf(mx4[2], s[i + 2]);
-                mx4[3] = fmaxf(mx4[3], s[i + 3]);
+            for (int i = 0; i < HALF_K; i += 8) {
+                mx4[0] = max3(mx4[0], s[i], s[i + 1]);
+                mx4[1] = max3(mx4[1], s[i + 2], s[i + 3]);
+                mx4[2] = max3(mx4[2], s[i + 4], s[i + 5]);
+                mx4[3] = max3(mx4[3], s[i + 6], s[i + 7]);
             }
             // The row's other half: through shared memory and the pair's barrier.  Both sides
             // round to bfloat16, so that both scale by the same number (the scaling maximum
@@ -348,15 +374,18 @@ attn_prompt_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_co
                     tc_st_wait();
                 }
             }
-            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            float2 sum2[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
             uint32_t packed[HALF_K / 2];
+            const float2 sl2_2 = make_float2(sl2, sl2), neg_m2 = make_float2(neg_m, neg_m);
 #pragma unroll
             for (int i = 0; i < HALF_K; i += 2) {
-                const float p0 = ex2(fmaf(s[i], sl2, neg_m)), p1 = ex2(fmaf(s[i + 1], sl2, neg_m));
-                sum4[(i >> 1) & 3] += p0 + p1;
-                __nv_bfloat162 hh = __floats2bfloat162_rn(p0, p1);          // key 2k in the low half, key 2k + 1 in the high half
+                const float2 x = fma2(make_float2(s[i], s[i + 1]), sl2_2, neg_m2);
+                const float2 pp = make_float2(ex2(x.x), ex2(x.y));
+                sum2[(i >> 1) & 3] = add2(sum2[(i >> 1) & 3], pp);
+                __nv_bfloat162 hh = __floats2bfloat162_rn(pp.x, pp.y);      // key 2k in the low half, key 2k + 1 in the high half
                 packed[i >> 1] = *reinterpret_cast<uint32_t*>(&hh);
             }
+            const float sum4[4] = {sum2[0].x + sum2[0].y, sum2[1].x + sum2[1].y, sum2[2].x + sum2[2].y, sum2[3].x + sum2[3].y};
             // P over the scores it came from (the other half has its scores in registers: it passed the pair's barrier)
             tc_st32(s_addr + half * (HALF_K / 2), packed);
             tc_st_wait();
