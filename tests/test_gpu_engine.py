@@ -513,8 +513,9 @@ def test_prompt_steps_replayed_from_captured_steps_of_padded_sizes(dtype):
     tokens and what page 0 holds (NaN here) change no row; a step that is longer, or that
     continues a sequence beyond 512 positions, is launched kernel by kernel."""
     name = "D"
-    eng = make_engine(name, dtype, max_tokens=4096)
-    assert eng.prompt_graphs and eng.use_graphs
+    eng = make_engine(name, dtype, max_tokens=4096, use_graphs=True)
+    assert eng.model.prompt_capturable()
+    eng.prompt_graphs = True                                   # (whatever the environment's switches say)
     poison_all(eng)
     V = vocab_of(name)
 
@@ -569,7 +570,7 @@ def test_a_captured_prompt_step_and_the_same_step_launched_give_the_same_logits(
     seqs = [random_tokens(V, n, 400 + n) for n in (90, 3, 33)]
     out = []
     for captured in (True, False):
-        eng = make_engine(name, "bfloat16")
+        eng = make_engine(name, "bfloat16", use_graphs=True)
         eng.prompt_graphs = captured
         slots = [eng.open_seq() for _ in seqs]
         out.append(eng.step(slots, seqs).float().cpu())

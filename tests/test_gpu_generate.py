@@ -221,7 +221,7 @@ def test_a_shrinking_batch_that_ends_soon_keeps_its_captured_step():
     stops = [free[0].tokens[3], free[1].tokens[8], free[3].tokens[14]]
     opts = wick.GenOptions(max_tokens=30, sampler=wick.SamplerConfig.greedy(), stop_token_ids=stops)
     want = wick.generate(eng, prompts, opts, sampler_factory=wick.Sampler)
-    eng2 = make_engine("D", "bfloat16", std=STD, max_tokens=64 * 40)
+    eng2 = make_engine("D", "bfloat16", std=STD, max_tokens=64 * 40, use_graphs=True)
     got = wick.generate(eng2, prompts, opts)
     assert [(r.tokens, r.finish) for r in got] == [(r.tokens, r.finish) for r in want]
     assert len({len(r.tokens) for r in got}) > 2, "the requests end at different times"
