@@ -241,6 +241,8 @@ def test_prompt_attention_on_tcgen05(ops, heads, kv_heads, hd):
     sequence, lengths around the 128-key step, scrambled pages, NaN wherever the cache
     holds no token, and scores whose maximum jumps far up late in a row (so that the
     accumulator in tensor memory is rescaled) and early in a row (so that it is not)."""
+    if ops.plain_kernels():
+        pytest.skip("WICK_B200_PLAIN is set: this test is about a fast kernel, which the switch takes out")
     assert ops.attention_prompt_kind(hd, torch.bfloat16) == "tc"
     torch.manual_seed(hd + heads)
     q_lens, starts = [300, 128, 1, 129, 257], [77, 0, 500, 127, 0]
@@ -706,6 +708,8 @@ def test_cuda_core_decode_attention_cuts_a_length_back_to_its_table(ops, dtype):
     """A length one split beyond what the call was sized for: the kernel reports it and works
     on what the page table and the scratch hold (the cache and the table given here are large
     enough that even an unguarded kernel would have stayed inside them)."""
+    if ops.plain_kernels():
+        pytest.skip("WICK_B200_PLAIN is set: this test is about a fast kernel, which the switch takes out")
     heads, kv_heads, hd = 4, 2, 32
     split = ops.attention_decode_split(hd, dtype)
     n = 2 * split
