@@ -229,3 +229,26 @@ def test_a_shrinking_batch_that_ends_soon_keeps_its_captured_step():
     assert captured == [(8, 8)], captured
     long = wick.generate(eng2, [prompts[0]], wick.GenOptions(max_tokens=200, sampler=wick.SamplerConfig.greedy()))
     assert len(long[0].tokens) == 200 and (1, 8) in {k for k, g in eng2._graphs.items() if g.graph is not None}
+
+
+def test_warm_up_captures_what_generation_would():
+    """Engine.warm_up captures the decode steps and the short prompt steps ahead of time;
+    a generation within those sizes then captures nothing more, and gives what it gives on an
+    engine that was not warmed up."""
+    eng = make_engine("D", "bfloat16", std=STD, max_tokens=64 * 40, use_graphs=True)
+    n = eng.warm_up(max_batch=5, context=300, prompt_tokens=128)
+    decode = sorted(k for k, g in eng._graphs.items() if g.graph is not None)
+    assert decode == [(1, 8), (2, 8), (4, 8), (8, 8)], decode
+    assert sorted(eng._prompt_graphs) == [(t, b + 1, b + 1) for t in (64, 128) for b in (1, 2, 4, 8)]
+    assert n == len(decode) + len(eng._prompt_graphs)
+    assert eng.warm_up(max_batch=5, context=300, prompt_tokens=128) == 0
+    eng.cache.check()
+    prompts = [random_tokens(640, k, 900 + k) for k in (12, 5, 30, 7, 3)]
+    opts = wick.GenOptions(max_tokens=20, sampler=wick.SamplerConfig.greedy())
+    got = wick.generate(eng, prompts, opts)
+    assert sorted(k for k, g in eng._graphs.items() if g.graph is not None) == decode and len(eng._prompt_graphs) == 8
+    cold = make_engine("D", "bfloat16", std=STD, max_tokens=64 * 40, use_graphs=True)
+    want = wick.generate(cold, prompts, opts)
+    assert [(r.tokens, r.finish) for r in got] == [(r.tokens, r.finish) for r in want]
+    off = make_engine("D", "bfloat16", std=STD, max_tokens=64 * 40, use_graphs=False)
+    assert off.warm_up(max_batch=5) == 0

@@ -177,6 +177,34 @@ class Engine:
         self._steps_since_check = 0
         ops.check_status()
 
+    def warm_up(self, max_batch: int = 1, context: Optional[int] = None, prompt_tokens: int = 0) -> int:
+        """Capture now what generation would capture on first use: the decode steps of every
+        padded batch size up to ``max_batch`` and every page-table width up to ``context``
+        positions (default: what the cache can hold per sequence), and the prompt steps of one
+        to ``max_batch`` sequences of up to ``prompt_tokens`` tokens together (at most 512: longer
+        steps are not captured).  Touches only the reserved page and slot.  Returns how many
+        steps were captured; with graphs switched off it captures nothing."""
+        if not self.use_graphs:
+            return 0
+        before = sum(g.graph is not None for g in self._graphs.values()) + len(self._prompt_graphs)
+        context = min(context or self.spec.max_position, self.spec.max_position, self.cache.max_tokens)
+        batches = sorted({self._bucket(b) for b in range(1, max(1, max_batch) + 1)})
+        pages, widths = (context + PAGE - 1) // PAGE, []
+        w = 8
+        while True:
+            widths.append(w)
+            if w >= pages:
+                break
+            w *= 2
+        for b in batches:
+            for w in widths:
+                self._decode_graph(b, w)
+        for t in range(PAGE, min(prompt_tokens, PROMPT_GRAPH_TOKENS) + PAGE, PAGE):
+            for b in batches:
+                if b <= min(t, PROMPT_GRAPH_SEQS):
+                    self._prompt_graph([t - b + 1] + [1] * (b - 1), [t - b + 1] + [1] * (b - 1), b)
+        return sum(g.graph is not None for g in self._graphs.values()) + len(self._prompt_graphs) - before
+
     # ---- sequences ---------------------------------------------------------
     def open_seq(self) -> int:
         return self.cache.open_seq()
