@@ -230,6 +230,7 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="no batch 1 / 64 runs")
     ap.add_argument("--skip-models", action="store_true", help="no 14b / 32b workloads")
     ap.add_argument("--skip-e2e", action="store_true", help="no run through the Python entry point")
+    ap.add_argument("--prefill-steps", type=int, default=0, help="timed prompt steps (default: about a second's worth, at most 40)")
     ap.add_argument("--skip-prefill", action="store_true")
     ap.add_argument("--skip-decode", action="store_true", help="prefill only (for profiling)")
     ap.add_argument("--eager", action="store_true", help="no CUDA graphs (every kernel is a launch of its own)")
@@ -320,7 +321,7 @@ def main() -> int:
     # step is timed in the same state: after 3 warm-up steps, a second or so of steps back to back (the first
     # steps of a product-heavy phase run at the part's full clock, the next ones while the power control settles).
     pf_warm = 3
-    pf_timed = 0 if args.skip_prefill else max(5, min(40, int(40 * 2048 / max(n_prefill, 1))))
+    pf_timed = 0 if args.skip_prefill else (args.prefill_steps or max(5, min(40, int(40 * 2048 / max(n_prefill, 1)))))
     for i in range(0 if args.skip_prefill else pf_warm + pf_timed):
         s = eng.open_seq()
         torch.cuda.synchronize()
